@@ -1,0 +1,266 @@
+/* b200graft: the C ABI of the B200-native hot path (dense GEMM with fused
+ * epilogue, weight-only int8/int4 dequant-matmul, row reductions, and the
+ * Qwen3-shaped int4 decoder step built from them).
+ *
+ * Conventions, kept from the reference's XLA-free dispatch functions (the seam
+ * its FFI handlers and BlasLt plan call into, e.g. metal_pjrt/ffi/scan.h:45-48,
+ * metal_pjrt/blas/steel_gemm.h:72-78):
+ *   - every buffer is a BORROWED raw device pointer; the library never owns or
+ *     frees caller memory; the caller owns the stream;
+ *   - every call only enqueues on `stream` and returns; no host sync, no hidden
+ *     allocation on the hot path (the reference GEMM reports workspace 0,
+ *     metal_pjrt/blas/metal_blas.cc:425-431);
+ *   - errors are status codes with a thread-local message, never aborts
+ *     (status vocabulary of metal_pjrt/runtime/metal_runtime.h:33-41);
+ *     anything unsupported is refused before any launch;
+ *   - zero-sized problems launch nothing and succeed (metal_blas.cc:383);
+ *   - the first failure makes the context's error sticky: every later call on
+ *     that context returns it (metal_pjrt/runtime/metal_runtime.h:43-53).
+ * There is no CPU fallback anywhere behind this header.
+ */
+#ifndef B200GRAFT_H_
+#define B200GRAFT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+typedef enum {
+  B200_OK = 0,
+  B200_INVALID_ARGUMENT = 1,    /* caller mistake */
+  B200_UNIMPLEMENTED = 2,       /* known gap, refused up front */
+  B200_INTERNAL = 3,            /* CUDA API failure */
+  B200_RESOURCE_EXHAUSTED = 4,
+  B200_FAILED_PRECONDITION = 5,
+  B200_TIMEOUT = 6              /* a bounded device-side wait ran out */
+} b200_status;
+
+typedef enum { B200_F32 = 0, B200_F16 = 1, B200_BF16 = 2 } b200_dtype;
+
+typedef struct b200_context b200_context;
+typedef struct CUstream_st* b200_stream; /* == cudaStream_t */
+
+/* ---- context -------------------------------------------------------------
+ * Replaces rt::Device (metal_pjrt/runtime/metal_runtime.h:276-450) with the
+ * little a CUDA caller needs: device ordinal, attribute cache, a device status
+ * word, the sticky error. */
+int b200_abi_version(void); /* ≙ metal_pjrt_frontend_abi_version, metal_pjrt/pjrt/metal_pjrt_api.cc:390-392 */
+b200_status b200_context_create(int device_ordinal, b200_context** out);
+void b200_context_destroy(b200_context* ctx);
+/* Message of the last failing call on this thread (valid until the next call). */
+const char* b200_last_error(void);
+/* The sticky error; also folds in the device status word (a kernel whose bounded
+ * wait ran out reports B200_TIMEOUT here).  Synchronises nothing: call after
+ * the stream was synchronised to see device-side reports. */
+b200_status b200_context_error(b200_context* ctx);
+/* Host-side fault injection (≙ METAL_PJRT_FAIL_COMMAND_BUFFER=n,
+ * metal_pjrt/runtime/metal_runtime.cc:1646-1653): the n-th launch from now
+ * (1 = next) is refused before it is enqueued and sets the sticky error.
+ * n <= 0 disarms. */
+void b200_context_fail_launch_after(b200_context* ctx, int64_t n);
+/* Number of kernels this context has enqueued so far. */
+int64_t b200_context_launch_count(b200_context* ctx);
+
+/* ---- dense GEMM ------------------------------------------------------------
+ * GemmParams / MpsOperand (metal_pjrt/blas/mps_gemm.h:23-53) and SteelEpilogue
+ * (metal_pjrt/blas/steel_gemm.h:38-46): row-major
+ *   D[b] (m x n) = act(alpha * op(A[b]) op(B[b]) + beta * D[b] + bias[col]),
+ * aux = the pre-activation value; f32 accumulation, one rounding. */
+typedef struct {
+  void* ptr;            /* element (0,0) of batch 0 */
+  int64_t ld;           /* elements between consecutive stored rows */
+  int64_t batch_stride; /* elements between batches; 0 = broadcast */
+  int32_t dtype;        /* b200_dtype */
+  int32_t transpose;    /* operand is used as op(X) = X^T */
+} b200_operand;
+
+typedef struct {
+  int64_t m, n, k, batch;
+  double alpha, beta;
+  b200_operand a, b, c; /* c is both the beta input and the output D */
+} b200_gemm_params;
+
+typedef struct {
+  int32_t act;      /* 0 none, 1 ReLU (keeps NaN), 2 GELU-tanh, 3 SiLU */
+  const void* bias; /* n elements of D's dtype, or NULL */
+  void* aux;        /* D's layout and dtype, or NULL */
+} b200_epilogue;
+
+/* ≙ SteelGemmSupports + RunSteelGemm's argument checks
+ * (metal_pjrt/blas/steel_gemm.cc:140-196) and the size limits of ValidateMatmul
+ * (metal_pjrt/blas/blas_lt_support.cc:167-190).  Pure. */
+b200_status b200_gemm_validate(const b200_gemm_params* p, const b200_epilogue* epi);
+/* ≙ RunHalfGemm / RunSteelGemm / RunGemv / RunMpsGemm + epilogue
+ * (metal_pjrt/blas/metal_blas.cc:91-118, steel_gemm.cc:163-255, gemv.cc:129-196). */
+b200_status b200_gemm(b200_context* ctx, b200_stream stream, const b200_gemm_params* p,
+                      const b200_epilogue* epi);
+/* Which kernel b200_gemm would run (≙ ChooseGemv / ChooseSteelTile,
+ * gemv.cc:68-108, steel_gemm.cc:115-138): 0 nothing (empty problem),
+ * 1 tcgen05 tensor-core tile kernel, 2 few-row streaming kernel, 3 SIMT tile kernel. */
+typedef enum { B200_ROUTE_NONE = 0, B200_ROUTE_TCGEN05 = 1, B200_ROUTE_FEWROW = 2,
+               B200_ROUTE_SIMT = 3 } b200_gemm_route_t;
+int b200_gemm_route(const b200_gemm_params* p, const b200_epilogue* epi);
+/* ≙ GemmWork (metal_pjrt/blas/mps_gemm_objc.cc:57-67): max(2 b m n k, 64 * bytes). */
+uint64_t b200_gemm_work(const b200_gemm_params* p);
+/* A/B switch for benchmarks and tests (≙ RunSteelGemm's explicit tile argument,
+ * steel_gemm.h:72-78): force a route (b200_gemm_route_t), 0 = automatic. */
+void b200_gemm_force_route(b200_context* ctx, int route);
+
+/* ---- weight-only quantised matmul ------------------------------------------
+ * out[M, N] = x[M, K] . dequant(W)[N, K]^T, W stored [N, K] with K contiguous
+ * (the reference keeps [out, in], examples/llm/qwen3.py:102).  The reference has
+ * no kernel for this; the math is that of _matvec_int8/_matvec_int4 and
+ * dequantize (examples/llm/qwen3.py:199-267): w = q*s (+ b), all in f32, one
+ * rounding to the activation dtype.
+ *   bits 16: q is a bf16 [N, K] matrix, no scale (the LM head / bf16 weights).
+ *   bits 8 : q int8 [N, K]; scale bf16 [N, K/group]; group == K is per-channel.
+ *   bits 4 : nibble_order 0: q uint32 [N, K/8], element k=8i+j at bits 4j..4j+3;
+ *            nibble_order 1: q uint8 [N, K/64, 32], low nibble = element j of the
+ *            group, high nibble = element j+32 (qwen3.py:169-196);
+ *            scale, bias bf16 [N, K/64].
+ * M <= 32 runs the streaming kernel; larger M is refused (dequantise, then GEMM,
+ * like the reference beyond ROWS_MAX, qwen3.py:210-230). */
+typedef enum { B200_QMM_OUT_BF16 = 0,      /* out bf16 [M, ldo] */
+               B200_QMM_ADD_RESIDUAL = 1,  /* out = bf16(residual + bf16(y)), residual bf16 [M, ldo] */
+               B200_QMM_OUT_F32 = 2,       /* out f32 [M, ldo] holding the bf16-rounded value */
+               B200_QMM_OUT_F32_RAW = 3    /* out f32 [M, ldo], unrounded (a partial sum of a K-sharded product) */
+} b200_qmm_epilogue;
+
+typedef struct {
+  int32_t bits;          /* 4, 8 or 16 */
+  int32_t group;         /* 64, or K (per output channel; int8 only) */
+  int32_t nibble_order;  /* bits == 4 only */
+  int32_t epilogue;      /* b200_qmm_epilogue */
+  const void* x;         /* bf16 [M, ldx] */
+  const void* q;
+  const void* scale;     /* NULL for bits 16 */
+  const void* bias;      /* bits 4 only */
+  const void* residual;  /* B200_QMM_ADD_RESIDUAL only; may alias out */
+  void* out;
+  int64_t M, N, K;
+  int64_t ldx, ldo;      /* 0 = dense (K and N) */
+} b200_qmm_params;
+
+b200_status b200_qmm_validate(const b200_qmm_params* p);
+b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_params* p);
+/* The short form: dense rows, bf16 in and out. */
+b200_status b200_qmm(b200_context* ctx, b200_stream stream, int bits, int group, int nibble_order,
+                     const void* x, const void* q, const void* scale, const void* bias_or_null,
+                     void* out, int64_t M, int64_t N, int64_t K, int act_dtype);
+/* How b200_qmm_run would tile this problem: rows per CTA, CTAs along K (cluster
+ * size), batch blocks of 8.  Pure; for tests and benchmarks. */
+b200_status b200_qmm_plan(const b200_qmm_params* p, int* rows_per_cta, int* split_k, int* batch_blocks);
+/* Dequantised weights written out, w[N, K] = q*s (+ b) in f32 with one rounding
+ * per operation, then stored as f32 (out_dtype B200_F32) or rounded once more to
+ * bf16 (≙ dequantize, qwen3.py:199-207).  The bit-exactness check reads this. */
+b200_status b200_dequantize(b200_context* ctx, b200_stream stream, int bits, int group, int nibble_order,
+                            const void* q, const void* scale, const void* bias_or_null, void* w_out,
+                            int64_t N, int64_t K, int out_dtype);
+/* Load-time quantisers on the device (≙ quantize_int8/quantize_int4,
+ * qwen3.py:154-196, in the benchmark's variants): w f32 or bf16 [N, K] ->
+ * int8 per-group symmetric (group == K: per channel), or int4 min/max affine
+ * with sequential uint32 nibbles.  scale/bias are written as bf16. */
+b200_status b200_quantize(b200_context* ctx, b200_stream stream, int bits, int group, const void* w,
+                          int w_dtype, void* q_out, void* scale_out, void* bias_out, int64_t N, int64_t K);
+
+/* ---- row reductions over the minor dimension --------------------------------
+ * kind 0 RMSNorm  y = x * rsqrt(mean(x^2) + eps) * gain   (examples/llm/qwen3.py:294-297)
+ *      1 softmax, 2 log_softmax (max-subtract form; call sites qwen3.py:325, tests/test_scan.py:35-48)
+ *      3 LayerNorm y = (x - mean) / sqrt(var + eps) [* gain + beta] (bench/jax_bench.py:44-46)
+ * Statistics in f32, one rounding to the input dtype.  x, y [rows, n] dense;
+ * y may alias x.  gain/beta have x's dtype. */
+b200_status b200_rownorm(b200_context* ctx, b200_stream stream, int kind, const void* x,
+                         const void* gain_or_null, const void* beta_or_null, void* y, int64_t rows,
+                         int64_t n, int dtype, double eps);
+
+/* ---- decoder step -------------------------------------------------------------
+ * One decode step (one new token per sequence) of the Qwen3-shaped decoder of
+ * examples/llm/qwen3.py:334-390, with int4-g64 projections (sequential uint32
+ * nibbles), bf16 activations, a bf16 KV cache laid out as the reference's
+ * (K [B, KV, S, D], V [B, KV, D, S], qwen3.py:279-291) and an untied bf16 LM
+ * head.  With tp_world > 1 each rank holds its shard (see b200_tp_*). */
+typedef struct {
+  int32_t layers, hidden, heads, kv_heads, head_dim, inter, vocab, max_len;
+  float rope_theta, rms_eps;
+  int32_t max_batch;
+} b200_decoder_config;
+
+typedef struct {             /* one projection, int4-g64 sequential layout */
+  const void* q;             /* uint32 [N, K/8] */
+  const void* scale;         /* bf16 [N, K/64] */
+  const void* bias;          /* bf16 [N, K/64] */
+} b200_qweight;
+
+typedef struct {
+  const void* attn_norm;     /* bf16 [hidden] */
+  b200_qweight qkv;          /* N = (heads + 2 kv_heads) * head_dim (this rank's heads) */
+  const void* q_norm;        /* bf16 [head_dim] */
+  const void* k_norm;
+  b200_qweight o;            /* N = hidden, K = heads * head_dim (this rank's heads) */
+  const void* mlp_norm;
+  b200_qweight gate_up;      /* N = 2 * inter (this rank's share: gate rows then up rows) */
+  b200_qweight down;         /* N = hidden, K = inter (this rank's share) */
+  void* k_cache;             /* bf16 [B, kv_heads, max_len, head_dim] */
+  void* v_cache;             /* bf16 [B, kv_heads, head_dim, max_len] */
+} b200_decoder_layer;
+
+typedef struct b200_decoder b200_decoder;
+typedef struct b200_tp b200_tp;
+
+/* cfg holds this rank's LOCAL head counts / inter / vocab share; `tp` may be NULL
+ * (one GPU).  The layer structs are copied; the buffers they point to are borrowed. */
+b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cfg,
+                                const b200_decoder_layer* layers, const void* embed /* bf16 [vocab_full, hidden] */,
+                                const void* final_norm, const void* lm_head /* bf16 [vocab, hidden] */,
+                                b200_tp* tp, b200_decoder** out);
+void b200_decoder_destroy(b200_decoder* dec);
+/* tokens: device int32 [batch]; pos: device int32 [1] (position of the new token,
+ * every sequence the same, qwen3.py:356); logits: device f32 [batch, vocab_total]
+ * (with tp: the all-gathered logits, rank-major).  Enqueues on `stream`; the
+ * first call for a batch size captures a CUDA graph, later calls replay it. */
+b200_status b200_decoder_step(b200_decoder* dec, b200_stream stream, const int32_t* tokens,
+                              const int32_t* pos, float* logits, int batch);
+/* Kernels enqueued by one step at this batch size (graph nodes). */
+int64_t b200_decoder_launches_per_step(b200_decoder* dec, int batch);
+
+/* Pieces of the step, exported for parity tests (bf16 throughout). */
+b200_status b200_embed(b200_context* ctx, b200_stream stream, const void* table, const int32_t* tokens,
+                       void* out, int64_t batch, int64_t hidden);
+/* Per-head RMSNorm + rotate-half RoPE of q and k, and the KV-cache write at *pos
+ * (qwen3.py:366-369).  qkv bf16 [B, (H + 2 KV) * D]; q_out bf16 [B, H, D]. */
+b200_status b200_qk_norm_rope_cache(b200_context* ctx, b200_stream stream, const void* qkv,
+                                    const void* q_norm, const void* k_norm, void* q_out, void* k_cache,
+                                    void* v_cache, const int32_t* pos, int64_t batch, int heads,
+                                    int kv_heads, int head_dim, int64_t max_len, float theta, float eps);
+/* Grouped-query decode attention over slots [0, *pos] (qwen3.py:322-327).
+ * scratch: f32, b200_attention_scratch_bytes(...) bytes. */
+size_t b200_attention_scratch_bytes(int64_t batch, int heads, int head_dim, int64_t max_len);
+b200_status b200_attention_decode(b200_context* ctx, b200_stream stream, const void* q, const void* k_cache,
+                                  const void* v_cache, void* out, const int32_t* pos, void* scratch,
+                                  int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_len);
+/* silu(gate) * up with the reference's bf16 roundings (qwen3.py:376). gate_up bf16 [B, 2*inter]. */
+b200_status b200_silu_mul(b200_context* ctx, b200_stream stream, const void* gate_up, void* out,
+                          int64_t batch, int64_t inter);
+
+/* ---- tensor parallel group (NEW: the reference is single-device,
+ * metal_pjrt/compiler/metal_collectives_registration.cc:10-17) ------------------
+ * One process per GPU.  Rank 0 makes an id, the caller distributes its bytes
+ * (any transport), every rank calls b200_tp_create. */
+#define B200_TP_ID_BYTES 128
+b200_status b200_tp_make_id(void* id_bytes /* B200_TP_ID_BYTES */);
+b200_status b200_tp_create(b200_context* ctx, const void* id_bytes, int rank, int world, b200_tp** out);
+void b200_tp_destroy(b200_tp* tp);
+/* In-place sum over ranks of a bf16 [count] buffer; all-gather of `count` f32 per rank. */
+b200_status b200_tp_all_reduce_bf16(b200_tp* tp, b200_stream stream, void* buf, int64_t count);
+b200_status b200_tp_all_gather_f32(b200_tp* tp, b200_stream stream, const void* send, void* recv,
+                                   int64_t count_per_rank);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GRAFT_H_ */

@@ -1,0 +1,153 @@
+// Context, status and error plumbing of the C ABI (see include/b200graft.h).
+// Replaces the reference's rt::Device error model (sticky first error,
+// metal_pjrt/runtime/metal_runtime.h:43-53) and its host-side fault
+// injection (metal_pjrt/runtime/metal_runtime.cc:1646-1653).
+#include "common.cuh"
+
+namespace b200 {
+
+static thread_local char g_error[1024] = "";
+
+void SetError(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+b200_status Fail(b200_status code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+b200_status Stick(b200_context* ctx, b200_status code) {
+  if (ctx == nullptr || code == B200_OK) return code;
+  int expected = 0;
+  if (ctx->sticky.compare_exchange_strong(expected, static_cast<int>(code))) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->sticky_message = g_error;
+  }
+  return code;
+}
+
+b200_status BeginLaunch(b200_context* ctx) {
+  if (ctx == nullptr) return Fail(B200_INVALID_ARGUMENT, "null context");
+  const int sticky = ctx->sticky.load();
+  if (sticky != 0) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    SetError("context is in a failed state: %s", ctx->sticky_message.c_str());
+    return static_cast<b200_status>(sticky);
+  }
+  const int64_t fail_at = ctx->fail_at.load();
+  if (fail_at > 0 && ctx->launches.load() + 1 >= fail_at) {
+    ctx->fail_at.store(0);
+    return Stick(ctx, Fail(B200_INTERNAL, "injected launch failure (launch %lld refused before enqueue)",
+                           static_cast<long long>(fail_at)));
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess)
+    return Stick(ctx, Fail(B200_INTERNAL, "cudaSetDevice(%d): %s", ctx->device, cudaGetErrorString(e)));
+  return B200_OK;
+}
+
+b200_status EndLaunch(b200_context* ctx, const char* what, int kernels) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "%s: %s", what, cudaGetErrorString(e)));
+  ctx->launches.fetch_add(kernels);
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_abi_version(void) { return B200_ABI_VERSION; }
+
+const char* b200_last_error(void) { return g_error; }
+
+b200_status b200_context_create(int device_ordinal, b200_context** out) {
+  if (out == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_context_create: null out");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    (void)cudaGetLastError();
+    return Fail(B200_FAILED_PRECONDITION, "no CUDA device: %s (this library has no CPU fallback)",
+                e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+  }
+  if (device_ordinal < 0 || device_ordinal >= count)
+    return Fail(B200_INVALID_ARGUMENT, "device ordinal %d out of range [0, %d)", device_ordinal, count);
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device_ordinal);
+  if (e != cudaSuccess) return Fail(B200_INTERNAL, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return Fail(B200_FAILED_PRECONDITION, "device %d is sm_%d%d; this library holds sm_100a code only",
+                device_ordinal, prop.major, prop.minor);
+  e = cudaSetDevice(device_ordinal);
+  if (e != cudaSuccess) return Fail(B200_INTERNAL, "cudaSetDevice: %s", cudaGetErrorString(e));
+  b200_context* ctx = new b200_context();
+  ctx->device = device_ordinal;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+  e = cudaMalloc(&ctx->dev_status, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&ctx->host_status, 4 * sizeof(int));
+  if (e != cudaSuccess) {
+    b200_status s = Fail(B200_RESOURCE_EXHAUSTED, "context allocation: %s", cudaGetErrorString(e));
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    delete ctx;
+    return s;
+  }
+  ctx->host_status[0] = 0;
+  *out = ctx;
+  return B200_OK;
+}
+
+void b200_context_destroy(b200_context* ctx) {
+  if (ctx == nullptr) return;
+  cudaSetDevice(ctx->device);
+  if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->host_status) cudaFreeHost(ctx->host_status);
+  delete ctx;
+}
+
+b200_status b200_context_error(b200_context* ctx) {
+  if (ctx == nullptr) return Fail(B200_INVALID_ARGUMENT, "null context");
+  int sticky = ctx->sticky.load();
+  if (sticky == 0 && ctx->dev_status != nullptr) {
+    // Plain blocking read of four ints; callers use this after synchronising.
+    int word[4] = {0, 0, 0, 0};
+    cudaSetDevice(ctx->device);
+    cudaError_t e = cudaMemcpy(word, ctx->dev_status, sizeof(word), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+      Stick(ctx, Fail(B200_INTERNAL, "reading the device status word: %s", cudaGetErrorString(e)));
+    } else if (word[0] != 0) {
+      Stick(ctx, Fail(static_cast<b200_status>(word[0]),
+                      "a kernel reported status %d (bounded wait %d gave up)", word[0], word[1]));
+    }
+    sticky = ctx->sticky.load();
+  }
+  if (sticky != 0) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    SetError("%s", ctx->sticky_message.c_str());
+  }
+  return static_cast<b200_status>(sticky);
+}
+
+void b200_context_fail_launch_after(b200_context* ctx, int64_t n) {
+  if (ctx == nullptr) return;
+  ctx->fail_at.store(n <= 0 ? 0 : ctx->launches.load() + n);
+}
+
+int64_t b200_context_launch_count(b200_context* ctx) { return ctx == nullptr ? 0 : ctx->launches.load(); }
+
+void b200_gemm_force_route(b200_context* ctx, int route) {
+  if (ctx != nullptr) ctx->force_route.store(route);
+}
+
+}  // extern "C"

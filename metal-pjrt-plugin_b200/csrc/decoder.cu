@@ -1,0 +1,298 @@
+// One decode step of the Qwen3-shaped int4 decoder
+// (examples/llm/qwen3.py:334-390 with T = 1), as a fixed sequence of this
+// library's kernels on one stream, captured once per batch size into a CUDA
+// graph (the launches carry programmatic-dependent-launch edges, so each
+// projection's weight stream starts while the kernel before it drains).
+//
+// With a tensor-parallel group the projections are sharded Megatron-style:
+// qkv and gate_up by output rows (heads / intermediate columns stay local, as
+// do the per-head norms, RoPE, the KV-cache shard and attention), o and down
+// by input columns, followed by an f32 all-reduce of the [B, hidden] partial
+// sums; the LM head by vocabulary rows, followed by an all-gather of logits.
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <tuple>
+#include <vector>
+
+#include "tp.cuh"
+
+using namespace b200;
+
+namespace {
+
+bool EnvFlag(const char* name) {
+  // Same grammar as the reference's EnvFlag (metal_pjrt/runtime/env.cc:17-22):
+  // unset, empty, 0, false, no, off (any case) are false; anything else is true.
+  const char* v = std::getenv(name);
+  if (v == nullptr) return false;
+  std::string s(v);
+  size_t b = s.find_first_not_of(" \t\n\r"), e = s.find_last_not_of(" \t\n\r");
+  s = b == std::string::npos ? "" : s.substr(b, e - b + 1);
+  for (char& c : s) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+  return !(s.empty() || s == "0" || s == "false" || s == "no" || s == "off");
+}
+
+// x = bf16(x + bf16(y)); h = rms_norm(x) * gain.  One CTA per row.  Used after
+// the all-reduce of a K-sharded projection (y holds the f32 sum over ranks).
+__global__ void residual_rmsnorm_kernel(__nv_bfloat16* x, const float* y, const __nv_bfloat16* gain,
+                                        __nv_bfloat16* h, int n, float eps) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * n;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = bf16_round(__bfloat162float(x[base + i]) + bf16_round(y[base + i]));
+    row[i] = v;
+    x[base + i] = __float2bfloat16_rn(v);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float t = (threadIdx.x & 31) < (blockDim.x >> 5) ? scratch[threadIdx.x & 31] : 0.0f;
+  t = warp_sum(t);
+  const float r = 1.0f / sqrtf(t / static_cast<float>(n) + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    h[base + i] = __float2bfloat16_rn((row[i] * r) * __bfloat162float(gain[i]));
+}
+
+}  // namespace
+
+struct b200_decoder {
+  b200_context* ctx = nullptr;
+  b200_decoder_config cfg = {};
+  std::vector<b200_decoder_layer> layers;
+  const void* embed = nullptr;
+  const void* final_norm = nullptr;
+  const void* lm_head = nullptr;
+  b200_tp* tp = nullptr;
+  // activations (device, sized for max_batch)
+  __nv_bfloat16 *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr,
+                *act = nullptr;
+  float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr;
+  bool use_graph = true;
+  std::map<std::tuple<int, const void*, const void*, const void*>, cudaGraphExec_t> graphs;
+  std::map<int, int64_t> launches;
+};
+
+namespace {
+
+b200_status Qmm(b200_decoder* d, cudaStream_t stream, const b200_qweight& w, const void* x, void* out, int batch,
+                int64_t N, int64_t K, int epilogue, const void* residual) {
+  b200_qmm_params p = {};
+  p.bits = 4;
+  p.group = 64;
+  p.nibble_order = 0;
+  p.epilogue = epilogue;
+  p.x = x;
+  p.q = w.q;
+  p.scale = w.scale;
+  p.bias = w.bias;
+  p.residual = residual;
+  p.out = out;
+  p.M = batch;
+  p.N = N;
+  p.K = K;
+  return b200_qmm_run(d->ctx, stream, &p);
+}
+
+b200_status ResidualNorm(b200_decoder* d, cudaStream_t stream, const void* gain, int batch) {
+  b200_status s = BeginLaunch(d->ctx);
+  if (s != B200_OK) return s;
+  LaunchCfg lc;
+  lc.stream = stream;
+  lc.pdl = true;
+  lc.grid = dim3(batch);
+  lc.block = dim3(256);
+  lc.smem = static_cast<size_t>(d->cfg.hidden) * 4;
+  cudaError_t e = Launch(lc, residual_rmsnorm_kernel, d->x, static_cast<const float*>(d->y32),
+                         static_cast<const __nv_bfloat16*>(gain), d->h, static_cast<int>(d->cfg.hidden),
+                         d->cfg.rms_eps);
+  if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "residual_rmsnorm launch: %s", cudaGetErrorString(e)));
+  return EndLaunch(d->ctx, "residual_rmsnorm");
+}
+
+#define B200_TRY(expr)                 \
+  do {                                 \
+    b200_status _s = (expr);           \
+    if (_s != B200_OK) return _s;      \
+  } while (0)
+
+b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens, const int32_t* pos, float* logits,
+                    int batch) {
+  const b200_decoder_config& c = d->cfg;
+  b200_context* ctx = d->ctx;
+  const int64_t E = c.hidden, HD = static_cast<int64_t>(c.heads) * c.head_dim;
+  const int64_t QKV = static_cast<int64_t>(c.heads + 2 * c.kv_heads) * c.head_dim;
+  const bool tp = d->tp != nullptr && d->tp->world > 1;
+
+  B200_TRY(b200_embed(ctx, stream, d->embed, tokens, d->x, batch, E));
+  B200_TRY(b200_rownorm(ctx, stream, 0, d->x, d->layers[0].attn_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
+  for (int li = 0; li < c.layers; ++li) {
+    const b200_decoder_layer& L = d->layers[li];
+    B200_TRY(Qmm(d, stream, L.qkv, d->h, d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr));
+    B200_TRY(b200_qk_norm_rope_cache(ctx, stream, d->qkv, L.q_norm, L.k_norm, d->q, L.k_cache, L.v_cache, pos, batch,
+                                     c.heads, c.kv_heads, c.head_dim, c.max_len, c.rope_theta, c.rms_eps));
+    B200_TRY(b200_attention_decode(ctx, stream, d->q, L.k_cache, L.v_cache, d->attn, pos, d->attn_scratch, batch,
+                                   c.heads, c.kv_heads, c.head_dim, c.max_len));
+    if (tp) {
+      B200_TRY(Qmm(d, stream, L.o, d->attn, d->y32, batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr));
+      B200_TRY(TpAllReduce(d->tp, stream, d->y32, static_cast<int64_t>(batch) * E, B200_F32));
+      B200_TRY(ResidualNorm(d, stream, L.mlp_norm, batch));
+    } else {
+      B200_TRY(Qmm(d, stream, L.o, d->attn, d->x, batch, E, HD, B200_QMM_ADD_RESIDUAL, d->x));
+      B200_TRY(b200_rownorm(ctx, stream, 0, d->x, L.mlp_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
+    }
+    B200_TRY(Qmm(d, stream, L.gate_up, d->h, d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
+                 nullptr));
+    B200_TRY(b200_silu_mul(ctx, stream, d->gu, d->act, batch, c.inter));
+    const void* next_norm = li + 1 < c.layers ? d->layers[li + 1].attn_norm : d->final_norm;
+    if (tp) {
+      B200_TRY(Qmm(d, stream, L.down, d->act, d->y32, batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr));
+      B200_TRY(TpAllReduce(d->tp, stream, d->y32, static_cast<int64_t>(batch) * E, B200_F32));
+      B200_TRY(ResidualNorm(d, stream, next_norm, batch));
+    } else {
+      B200_TRY(Qmm(d, stream, L.down, d->act, d->x, batch, E, c.inter, B200_QMM_ADD_RESIDUAL, d->x));
+      B200_TRY(b200_rownorm(ctx, stream, 0, d->x, next_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
+    }
+  }
+  // LM head: bf16 rows, logits are the bf16-rounded products widened to f32 (qwen3.py:389-390)
+  b200_qmm_params p = {};
+  p.bits = 16;
+  p.epilogue = B200_QMM_OUT_F32;
+  p.x = d->h;
+  p.q = d->lm_head;
+  p.out = tp ? d->logits_local : logits;
+  p.M = batch;
+  p.N = c.vocab;
+  p.K = E;
+  B200_TRY(b200_qmm_run(ctx, stream, &p));
+  if (tp) B200_TRY(TpAllGather(d->tp, stream, d->logits_local, logits, static_cast<int64_t>(batch) * c.vocab, B200_F32));
+  return B200_OK;
+}
+
+template <typename T>
+cudaError_t Alloc(T** p, size_t count) { return cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)); }
+
+}  // namespace
+
+extern "C" {
+
+b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cfg, const b200_decoder_layer* layers,
+                                const void* embed, const void* final_norm, const void* lm_head, b200_tp* tp,
+                                b200_decoder** out) {
+  if (out == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_decoder_create: null out");
+  *out = nullptr;
+  b200_status s = BeginLaunch(ctx);
+  if (s != B200_OK) return s;
+  if (cfg == nullptr || layers == nullptr || embed == nullptr || final_norm == nullptr || lm_head == nullptr)
+    return Fail(B200_INVALID_ARGUMENT, "b200_decoder_create: null argument");
+  const b200_decoder_config& c = *cfg;
+  if (c.layers <= 0 || c.hidden <= 0 || c.heads <= 0 || c.kv_heads <= 0 || c.inter <= 0 || c.vocab <= 0 ||
+      c.max_len <= 0 || c.max_batch <= 0)
+    return Fail(B200_INVALID_ARGUMENT, "b200_decoder_create: non-positive size");
+  if (c.max_batch > 32) return Fail(B200_UNIMPLEMENTED, "b200_decoder_create: max_batch %d (the decode path takes up to 32)", c.max_batch);
+  if (c.head_dim != 64 && c.head_dim != 128) return Fail(B200_UNIMPLEMENTED, "b200_decoder_create: head_dim %d", c.head_dim);
+  if (c.heads % c.kv_heads != 0) return Fail(B200_INVALID_ARGUMENT, "b200_decoder_create: heads not a multiple of kv_heads");
+  if (c.hidden % 64 != 0 || c.inter % 64 != 0 || (c.heads * c.head_dim) % 64 != 0)
+    return Fail(B200_UNIMPLEMENTED, "b200_decoder_create: hidden, inter and heads*head_dim must be multiples of 64");
+  b200_decoder* d = new b200_decoder();
+  d->ctx = ctx;
+  d->cfg = c;
+  d->layers.assign(layers, layers + c.layers);
+  d->embed = embed;
+  d->final_norm = final_norm;
+  d->lm_head = lm_head;
+  d->tp = tp;
+  d->use_graph = !EnvFlag("B200_DECODER_NO_GRAPH");
+  const size_t B = c.max_batch;
+  const size_t qkv = static_cast<size_t>(c.heads + 2 * c.kv_heads) * c.head_dim;
+  cudaError_t e = Alloc(&d->x, B * c.hidden);
+  if (e == cudaSuccess) e = Alloc(&d->h, B * c.hidden);
+  if (e == cudaSuccess) e = Alloc(&d->qkv, B * qkv);
+  if (e == cudaSuccess) e = Alloc(&d->q, B * c.heads * c.head_dim);
+  if (e == cudaSuccess) e = Alloc(&d->attn, B * c.heads * c.head_dim);
+  if (e == cudaSuccess) e = Alloc(&d->gu, B * 2 * c.inter);
+  if (e == cudaSuccess) e = Alloc(&d->act, B * static_cast<size_t>(c.inter));
+  if (e == cudaSuccess) e = Alloc(&d->y32, B * c.hidden);
+  if (e == cudaSuccess)
+    e = cudaMalloc(reinterpret_cast<void**>(&d->attn_scratch),
+                   b200_attention_scratch_bytes(c.max_batch, c.heads, c.head_dim, c.max_len));
+  if (e == cudaSuccess && tp != nullptr && tp->world > 1) e = Alloc(&d->logits_local, B * c.vocab);
+  if (e != cudaSuccess) {
+    s = Fail(B200_RESOURCE_EXHAUSTED, "b200_decoder_create: %s", cudaGetErrorString(e));
+    b200_decoder_destroy(d);
+    return s;
+  }
+  *out = d;
+  return B200_OK;
+}
+
+void b200_decoder_destroy(b200_decoder* d) {
+  if (d == nullptr) return;
+  cudaSetDevice(d->ctx->device);
+  for (auto& kv : d->graphs) cudaGraphExecDestroy(kv.second);
+  for (void* p : {static_cast<void*>(d->x), static_cast<void*>(d->h), static_cast<void*>(d->qkv),
+                  static_cast<void*>(d->q), static_cast<void*>(d->attn), static_cast<void*>(d->gu),
+                  static_cast<void*>(d->act), static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
+                  static_cast<void*>(d->logits_local)})
+    if (p != nullptr) cudaFree(p);
+  delete d;
+}
+
+b200_status b200_decoder_step(b200_decoder* d, b200_stream stream, const int32_t* tokens, const int32_t* pos,
+                              float* logits, int batch) {
+  if (d == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_decoder_step: null decoder");
+  b200_status s = BeginLaunch(d->ctx);
+  if (s != B200_OK) return s;
+  if (batch < 0 || batch > d->cfg.max_batch)
+    return Fail(B200_INVALID_ARGUMENT, "b200_decoder_step: batch %d outside [0, %d]", batch, d->cfg.max_batch);
+  if (batch == 0) return B200_OK;
+  if (tokens == nullptr || pos == nullptr || logits == nullptr)
+    return Fail(B200_INVALID_ARGUMENT, "b200_decoder_step: null buffer");
+  if (!d->use_graph) {
+    const int64_t before = d->ctx->launches.load();
+    s = Enqueue(d, stream, tokens, pos, logits, batch);
+    d->launches[batch] = d->ctx->launches.load() - before;
+    return s;
+  }
+  const auto key = std::make_tuple(batch, static_cast<const void*>(tokens), static_cast<const void*>(pos),
+                                   static_cast<const void*>(logits));
+  auto it = d->graphs.find(key);
+  if (it == d->graphs.end()) {
+    cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaStreamBeginCapture: %s", cudaGetErrorString(e)));
+    const int64_t before = d->ctx->launches.load();
+    s = Enqueue(d, stream, tokens, pos, logits, batch);
+    const int64_t count = d->ctx->launches.load() - before;
+    cudaGraph_t graph = nullptr;
+    e = cudaStreamEndCapture(stream, &graph);
+    if (s != B200_OK) {
+      if (graph != nullptr) cudaGraphDestroy(graph);
+      return s;
+    }
+    if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaStreamEndCapture: %s", cudaGetErrorString(e)));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaGraphInstantiate: %s", cudaGetErrorString(e)));
+    d->ctx->launches.fetch_sub(count);  // capture enqueued nothing; replays are counted below
+    d->launches[batch] = count;
+    it = d->graphs.emplace(key, exec).first;
+  }
+  cudaError_t e = cudaGraphLaunch(it->second, stream);
+  if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaGraphLaunch: %s", cudaGetErrorString(e)));
+  d->ctx->launches.fetch_add(d->launches[batch]);
+  return B200_OK;
+}
+
+int64_t b200_decoder_launches_per_step(b200_decoder* d, int batch) {
+  if (d == nullptr) return 0;
+  auto it = d->launches.find(batch);
+  return it == d->launches.end() ? 0 : it->second;
+}
+
+}  // extern "C"

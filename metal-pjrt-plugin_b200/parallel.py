@@ -1,0 +1,78 @@
+"""Tensor-parallel group and weight sharding for the decoder (new: the
+reference is single-device).  One process per GPU; torch.distributed moves the
+128-byte NCCL id and nothing else."""
+import ctypes as C
+
+from . import _lib
+from .context import default_context
+
+
+class TensorParallel:
+    def __init__(self, rank, world, id_bytes, ctx=None):
+        self.ctx = ctx or default_context()
+        self.rank, self.world = rank, world
+        handle = C.c_void_p()
+        buf = (C.c_char * _lib.TP_ID_BYTES).from_buffer_copy(id_bytes)
+        _lib.check(_lib.lib().b200_tp_create(self.ctx.handle, buf, rank, world, C.byref(handle)))
+        self.handle = handle
+
+    @staticmethod
+    def make_id():
+        buf = (C.c_char * _lib.TP_ID_BYTES)()
+        _lib.check(_lib.lib().b200_tp_make_id(buf))
+        return bytes(buf)
+
+    @classmethod
+    def from_torch_distributed(cls, ctx=None):
+        """Rank 0 makes the id; torch.distributed broadcasts it."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        box = [cls.make_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return cls(rank, world, box[0], ctx)
+
+    def all_reduce_bf16(self, t, stream=None):
+        _lib.check(_lib.lib().b200_tp_all_reduce_bf16(self.handle, stream or _lib.current_stream(), _lib.ptr(t), t.numel()))
+
+    def all_gather_f32(self, send, recv, stream=None):
+        _lib.check(_lib.lib().b200_tp_all_gather_f32(self.handle, stream or _lib.current_stream(), _lib.ptr(send),
+                                                     _lib.ptr(recv), send.numel()))
+
+    def close(self):
+        if self.handle:
+            _lib.lib().b200_tp_destroy(self.handle)
+            self.handle = None
+
+
+def shard_rows(n, rank, world):
+    """Contiguous block of n // world rows owned by `rank`."""
+    per = n // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+def local_config(cfg, world):
+    """Per-rank head / intermediate / vocab counts."""
+    for key in ("heads", "kv_heads", "inter", "vocab"):
+        if cfg[key] % world:
+            raise ValueError(f"{key}={cfg[key]} does not divide over {world} ranks")
+    out = dict(cfg)
+    out.update(heads=cfg["heads"] // world, kv_heads=cfg["kv_heads"] // world, inter=cfg["inter"] // world,
+               vocab=cfg["vocab"] // world)
+    return out
+
+
+def qkv_row_index(cfg, rank, world):
+    """Rows of the fused [q; k; v] matrix that rank owns (its query heads, its KV heads)."""
+    import numpy as np
+    H, KV, D = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    q = np.arange(H * D).reshape(world, -1)[rank]
+    k = H * D + np.arange(KV * D).reshape(world, -1)[rank]
+    v = (H + KV) * D + np.arange(KV * D).reshape(world, -1)[rank]
+    return np.concatenate([q, k, v])
+
+
+def gate_up_row_index(cfg, rank, world):
+    import numpy as np
+    inter = cfg["inter"]
+    g = np.arange(inter).reshape(world, -1)[rank]
+    return np.concatenate([g, inter + g])

@@ -1,0 +1,183 @@
+"""Model-level mirror of examples/llm/qwen3.py for the decode path: the same
+function names and argument meaning (quantize_int4 / quantize_int8 /
+dequantize / linear / rms_norm / init_cache / forward for T = 1), served by
+libb200graft.so.  Weights are dicts of torch CUDA tensors:
+
+    {"q4": int32 [N, K/8]  (uint32 words, k = 8i+j at bits 4j..4j+3), "s": bf16 [N, K/64], "b": bf16 [N, K/64]}
+    {"q4h": uint8 [N, K/64, 32] (the reference's split-half bytes),   "s": ..., "b": ...}
+    {"q": int8 [N, K], "s": bf16 [N, K/group]}          group == K: per output channel
+or a plain bf16 [N, K] tensor.  Nothing here computes on the host.
+"""
+import ctypes as C
+
+from . import _lib
+from .context import default_context
+from .rows import rms_norm  # noqa: F401  (qwen3.py:294-297)
+
+GROUP = 64
+ROWS_MAX = 32  # the streaming kernel's row limit (the reference's is 4, qwen3.py:215)
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def quantize_int4(w, group=GROUP, ctx=None):
+    """≙ quantize_int4 (qwen3.py:169-196) in the benchmark's min/max variant,
+    on the device. w: f32 or bf16 [N, K]."""
+    torch = _torch()
+    ctx = ctx or default_context()
+    N, K = w.shape
+    w = w.contiguous()
+    q = torch.empty((N, K // 8), dtype=torch.int32, device=w.device)
+    s = torch.empty((N, K // group), dtype=torch.bfloat16, device=w.device)
+    b = torch.empty_like(s)
+    _lib.check(_lib.lib().b200_quantize(ctx.handle, _lib.current_stream(), 4, group, _lib.ptr(w),
+                                        _lib.dtype_code(w.dtype), _lib.ptr(q), _lib.ptr(s), _lib.ptr(b), N, K))
+    return {"q4": q, "s": s, "b": b}
+
+
+def quantize_int8(w, group=None, ctx=None):
+    """≙ quantize_int8 (qwen3.py:154-166); group None = one scale per output channel."""
+    torch = _torch()
+    ctx = ctx or default_context()
+    N, K = w.shape
+    g = K if group is None else group
+    w = w.contiguous()
+    q = torch.empty((N, K), dtype=torch.int8, device=w.device)
+    s = torch.empty((N, K // g), dtype=torch.bfloat16, device=w.device)
+    _lib.check(_lib.lib().b200_quantize(ctx.handle, _lib.current_stream(), 8, g, _lib.ptr(w),
+                                        _lib.dtype_code(w.dtype), _lib.ptr(q), _lib.ptr(s), None, N, K))
+    return {"q": q, "s": s}
+
+
+def _describe(w):
+    """(bits, group, nibble_order, q, scale, bias, N, K) of a weight."""
+    if isinstance(w, dict):
+        if "q4" in w:
+            N, W = w["q4"].shape
+            return 4, 64, 0, w["q4"], w["s"], w["b"], N, W * 8
+        if "q4h" in w:
+            N, G, _ = w["q4h"].shape
+            return 4, 64, 1, w["q4h"], w["s"], w["b"], N, G * 64
+        N, K = w["q"].shape
+        return 8, K // w["s"].shape[1], 0, w["q"], w["s"], None, N, K
+    N, K = w.shape
+    return 16, 0, 0, w, None, None, N, K
+
+
+def dequantize(w, dtype=None, ctx=None):
+    """≙ dequantize (qwen3.py:199-207): the [out, in] matrix of a quantised
+    weight, f32 (one rounding per operation) or bf16."""
+    torch = _torch()
+    ctx = ctx or default_context()
+    bits, group, order, q, s, b, N, K = _describe(w)
+    dtype = dtype or torch.float32
+    out = torch.empty((N, K), dtype=dtype, device=q.device)
+    _lib.check(_lib.lib().b200_dequantize(ctx.handle, _lib.current_stream(), bits, group, order, _lib.ptr(q),
+                                          _lib.ptr(s), _lib.ptr(b), _lib.ptr(out), N, K, _lib.dtype_code(dtype)))
+    return out
+
+
+def linear(x, w, residual=None, out_f32=False, ctx=None, stream=None):
+    """≙ linear (qwen3.py:218-230): x @ w.T for an [out, in] weight, bf16 or
+    quantised, up to ROWS_MAX rows; result in x's dtype (bf16).  `residual`
+    fuses the x + linear(...) of the decoder layer; out_f32 gives the LM head's
+    f32 logits."""
+    torch = _torch()
+    ctx = ctx or default_context()
+    bits, group, order, q, s, b, N, K = _describe(w)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, K)
+    M = x2.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    p = _lib.QmmParamsC()
+    p.bits, p.group, p.nibble_order = bits, group, order
+    p.epilogue = _lib.QMM_OUT_F32 if out_f32 else (_lib.QMM_ADD_RESIDUAL if residual is not None else _lib.QMM_OUT_BF16)
+    p.x, p.q = x2.data_ptr(), q.data_ptr()
+    p.scale = s.data_ptr() if s is not None else None
+    p.bias = b.data_ptr() if b is not None else None
+    p.residual = residual.data_ptr() if residual is not None else None
+    p.out = out.data_ptr()
+    p.M, p.N, p.K = M, N, K
+    p.ldx, p.ldo = x2.stride(0) if M > 0 else K, N
+    _lib.check(_lib.lib().b200_qmm_run(ctx.handle, stream or _lib.current_stream(), C.byref(p)))
+    return out.reshape(*lead, N)
+
+
+def qmm_plan(M, N, K, bits=4, group=64):
+    """(rows per CTA, CTAs along K, batch blocks) the library would use."""
+    p = _lib.QmmParamsC()
+    p.bits, p.group, p.M, p.N, p.K = bits, group, M, N, K
+    p.x = p.q = p.scale = p.bias = p.out = 16  # non-null placeholders; nothing is dereferenced
+    r, s, m = C.c_int(), C.c_int(), C.c_int()
+    _lib.check(_lib.lib().b200_qmm_plan(C.byref(p), C.byref(r), C.byref(s), C.byref(m)))
+    return r.value, s.value, m.value
+
+
+def init_cache(cfg, batch, max_len, device="cuda"):
+    """≙ init_cache (qwen3.py:279-291): per-layer K [B, KV, S, D] and V [B, KV, D, S]."""
+    torch = _torch()
+    k = (batch, cfg["kv_heads"], max_len, cfg["head_dim"])
+    v = (batch, cfg["kv_heads"], cfg["head_dim"], max_len)
+    return {"k": [torch.zeros(k, dtype=torch.bfloat16, device=device) for _ in range(cfg["layers"])],
+            "v": [torch.zeros(v, dtype=torch.bfloat16, device=device) for _ in range(cfg["layers"])]}
+
+
+class Decoder:
+    """One-token decode step (≙ forward with T = 1, qwen3.py:334-390, driven like
+    generate.Engine.step, examples/llm/generate.py:146-148).  `params` follows
+    the reference's pytree: {"embed", "layers": [{"attn_norm", "qkv", "q_norm",
+    "k_norm", "o", "mlp_norm", "gate_up", "down"}], "norm", "lm_head"} with int4
+    ("q4") projections; `cache` comes from init_cache.  With `tp` the params and
+    cache hold this rank's shard and cfg the local head / intermediate / vocab
+    counts (see parallel.shard_params)."""
+
+    def __init__(self, params, cache, cfg, max_batch, ctx=None, tp=None):
+        self.ctx = ctx or default_context()
+        self.cfg, self.params, self.cache, self.tp = cfg, params, cache, tp
+        L = cfg["layers"]
+        max_len = cache["k"][0].shape[2]
+        cc = _lib.DecoderConfigC(L, cfg["hidden"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"],
+                                 cfg["vocab"], max_len, cfg["theta"], cfg["eps"], max_batch)
+        layers = (_lib.DecoderLayerC * L)()
+        for i, lp in enumerate(params["layers"]):
+            def qw(w):
+                return _lib.QWeightC(w["q4"].data_ptr(), w["s"].data_ptr(), w["b"].data_ptr())
+            layers[i] = _lib.DecoderLayerC(lp["attn_norm"].data_ptr(), qw(lp["qkv"]), lp["q_norm"].data_ptr(),
+                                           lp["k_norm"].data_ptr(), qw(lp["o"]), lp["mlp_norm"].data_ptr(),
+                                           qw(lp["gate_up"]), qw(lp["down"]), cache["k"][i].data_ptr(),
+                                           cache["v"][i].data_ptr())
+        handle = C.c_void_p()
+        _lib.check(_lib.lib().b200_decoder_create(self.ctx.handle, C.byref(cc), layers, params["embed"].data_ptr(),
+                                                  params["norm"].data_ptr(), params["lm_head"].data_ptr(),
+                                                  tp.handle if tp is not None else None, C.byref(handle)))
+        self.handle = handle
+        self.world = tp.world if tp is not None else 1
+
+    def step(self, tokens, pos, logits=None, stream=None):
+        """tokens int32 [B] (device), pos int32 [1] (device). Returns f32 logits
+        [B, V]; with tp [world, B, V/world] (rank-major)."""
+        torch = _torch()
+        B = tokens.shape[0]
+        if logits is None:
+            shape = (B, self.cfg["vocab"]) if self.world == 1 else (self.world, B, self.cfg["vocab"])
+            logits = torch.empty(shape, dtype=torch.float32, device=tokens.device)
+        _lib.check(_lib.lib().b200_decoder_step(self.handle, stream or _lib.current_stream(), _lib.ptr(tokens),
+                                                _lib.ptr(pos), _lib.ptr(logits), B))
+        return logits
+
+    def launches_per_step(self, batch):
+        return _lib.lib().b200_decoder_launches_per_step(self.handle, batch)
+
+    def close(self):
+        if self.handle:
+            _lib.lib().b200_decoder_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

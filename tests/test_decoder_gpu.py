@@ -1,0 +1,179 @@
+"""The decode step and its pieces on the device against the oracle and the
+fixtures recorded from the reference's forward()."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import decoder as odec
+from oracle import dense, inputs
+from util import bf16, dev, dev_params, host, pkg, rel_rms_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(p, fn, *args):
+    p._lib.check(fn(p.default_context().handle, p._lib.current_stream(), *args))
+
+
+def test_rope_norm_cache_and_attention_against_reference_fixture(golden_dir):
+    import torch
+    p = pkg()
+    L = p.lib()
+    z = np.load(os.path.join(golden_dir, "rows_ref.npz"))
+    # decode attention recorded from the reference: q [B,1,KV,G,D], K [B,KV,S,D], V [B,KV,D,S], 18 valid slots
+    q = z["q"].view(bf16)[:, 0]
+    B, KV, G, D = q.shape
+    S = z["kc"].shape[2]
+    qd, kd, vd = dev(q.reshape(B, KV * G, D)), dev(z["kc"].view(bf16)), dev(z["vc"].view(bf16))
+    out = torch.empty((B, KV * G, D), dtype=torch.bfloat16, device="cuda")
+    pos = torch.tensor([17], dtype=torch.int32, device="cuda")
+    scratch = torch.empty(L.b200_attention_scratch_bytes(B, KV * G, D, S) // 4, device="cuda")
+    _call(p, L.b200_attention_decode, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), pos.data_ptr(),
+          scratch.data_ptr(), B, KV * G, KV, D, S)
+    want = z["attn"].view(bf16)[:, 0].reshape(B, KV * G, D).astype(np.float32)
+    assert rel_rms_err(host(out).astype(np.float32), want) <= 2e-2
+
+
+@pytest.mark.parametrize("B,H,KV,D,S,pos", [(2, 4, 2, 64, 48, 30), (3, 8, 2, 128, 300, 299), (1, 32, 8, 128, 2176, 2048),
+                                            (2, 4, 4, 128, 130, 0)])
+def test_pieces_against_oracle(B, H, KV, D, S, pos):
+    import torch
+    p = pkg()
+    L = p.lib()
+    rng = np.random.default_rng(11)
+    qkv = rng.standard_normal((B, (H + 2 * KV) * D), dtype=np.float32).astype(bf16)
+    qn = (1 + 0.1 * rng.standard_normal(D, dtype=np.float32)).astype(bf16)
+    kn = (1 + 0.1 * rng.standard_normal(D, dtype=np.float32)).astype(bf16)
+    kc = rng.standard_normal((B, KV, S, D), dtype=np.float32).astype(bf16)
+    vc = rng.standard_normal((B, KV, D, S), dtype=np.float32).astype(bf16)
+    kd, vd = dev(kc), dev(vc)
+    qo = torch.empty((B, H, D), dtype=torch.bfloat16, device="cuda")
+    posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    _call(p, L.b200_qk_norm_rope_cache, dev(qkv).data_ptr(), dev(qn).data_ptr(), dev(kn).data_ptr(), qo.data_ptr(),
+          kd.data_ptr(), vd.data_ptr(), posd.data_ptr(), B, H, KV, D, S, 1e6, 1e-6)
+    from oracle.rownorm import rms_norm
+    positions = np.full((B,), pos)
+    q_ref = odec.rope(rms_norm(qkv[:, :H * D].reshape(B, H, D), qn, 1e-6), positions, 1e6)
+    k_ref = odec.rope(rms_norm(qkv[:, H * D:(H + KV) * D].reshape(B, KV, D), kn, 1e-6), positions, 1e6)
+    v_ref = qkv[:, (H + KV) * D:].reshape(B, KV, D)
+    assert rel_rms_err(host(qo).astype(np.float32), q_ref.astype(np.float32)) <= 2e-2
+    kc2, vc2 = kc.copy(), vc.copy()
+    kc2[:, :, pos] = k_ref
+    vc2[:, :, :, pos] = v_ref
+    gk, gv = host(kd), host(vd)
+    assert rel_rms_err(gk[:, :, pos].astype(np.float32), k_ref.astype(np.float32)) <= 2e-2
+    assert np.array_equal(gv[:, :, :, pos].view(np.uint16), v_ref.view(np.uint16))
+    mask = np.ones(S, bool)
+    mask[pos] = False   # every other slot untouched, bit for bit
+    assert np.array_equal(gk[:, :, mask].view(np.uint16), kc[:, :, mask].view(np.uint16))
+    assert np.array_equal(gv[:, :, :, mask].view(np.uint16), vc[:, :, :, mask].view(np.uint16))
+    # attention over the cache just written
+    out = torch.empty((B, H, D), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(L.b200_attention_scratch_bytes(B, H, D, S) // 4, device="cuda")
+    _call(p, L.b200_attention_decode, qo.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), posd.data_ptr(),
+          scratch.data_ptr(), B, H, KV, D, S)
+    a_ref = odec.attention_decode(host(qo).reshape(B, KV, H // KV, D), gk, gv, pos + 1, D ** -0.5)
+    assert rel_rms_err(host(out).astype(np.float32), a_ref.reshape(B, H, D).astype(np.float32)) <= 2e-2
+
+
+def test_silu_mul_and_embed():
+    import torch
+    p = pkg()
+    L = p.lib()
+    rng = np.random.default_rng(12)
+    gu = (rng.standard_normal((5, 2 * 384), dtype=np.float32) * 2).astype(bf16)
+    out = torch.empty((5, 384), dtype=torch.bfloat16, device="cuda")
+    _call(p, L.b200_silu_mul, dev(gu).data_ptr(), out.data_ptr(), 5, 384)
+    want = odec.silu_mul(gu[:, :384], gu[:, 384:])
+    got = host(out)
+    ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want.astype(np.float32)), 1e-30))) - 7)
+    assert np.all(np.abs(got.astype(np.float32) - want.astype(np.float32)) <= 1.01 * ulp)
+    table = rng.standard_normal((100, 256), dtype=np.float32).astype(bf16)
+    tok = np.array([3, 99, 0, 3], np.int32)
+    e = torch.empty((4, 256), dtype=torch.bfloat16, device="cuda")
+    _call(p, L.b200_embed, dev(table).data_ptr(), dev(tok).data_ptr(), e.data_ptr(), 4, 256)
+    assert np.array_equal(host(e).view(np.uint16), table[tok].view(np.uint16))
+
+
+def _run_decoder(cfg, batch, ctx, max_len, steps=1):
+    import torch
+    p = pkg()
+    params, cache, tokens = inputs.config5(cfg, batch, ctx, max_len=max_len)
+    ocache = {k: [a.copy() for a in v] for k, v in cache.items()}
+    dparams = dev_params(params)
+    dcache = {k: [dev(a) for a in v] for k, v in cache.items()}
+    dec = p.qwen3.Decoder(dparams, dcache, cfg, max_batch=batch)
+    tok = tokens
+    posd = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tokd = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    results = []
+    for st in range(steps):
+        pos = ctx + st
+        want = odec.decode_step(params, tok, ocache, pos, cfg)
+        tokd.copy_(dev(tok.astype(np.int32)))
+        posd.fill_(pos)
+        logits = dec.step(tokd, posd)
+        torch.cuda.synchronize()
+        results.append((host(logits), want))
+        tok = want.argmax(-1)
+    assert p.default_context().error() == 0
+    return results, dcache, ocache, dec
+
+
+@pytest.mark.parametrize("batch", [1, 8, 32])
+def test_decoder_step_small(batch):
+    cfg = inputs.decoder_config(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=512, vocab=2048)
+    results, dcache, ocache, dec = _run_decoder(cfg, batch, ctx=70, max_len=96, steps=2)
+    for got, want in results:
+        # two layers of bf16 activations: rounding flips compound (see the oracle's own C-vs-NumPy bound)
+        assert dense.max_abs_over_rms(got, want) <= 6e-2
+        assert np.mean(got.argmax(-1) == want.argmax(-1)) >= 0.9
+    for li in range(2):
+        assert rel_rms_err(host(dcache["k"][li]).astype(np.float32), ocache["k"][li].astype(np.float32)) <= 8e-2
+    assert dec.launches_per_step(batch) > 0
+
+
+def test_decoder_against_reference_fixture(golden_dir):
+    """The reference's forward() output (split-half int4 repacked to sequential words)."""
+    import torch
+    from oracle import quant
+    p = pkg()
+    z = np.load(os.path.join(golden_dir, "decoder_ref.npz"))
+    cfg = dict(layers=2, hidden=128, heads=4, kv_heads=2, head_dim=64, inter=256, vocab=320, theta=1e6, eps=1e-6)
+    layers = []
+    for li in range(2):
+        lp = {n: dev(z[f"l{li}_{n}"].view(bf16)) for n in ("attn_norm", "q_norm", "k_norm", "mlp_norm")}
+        for n in ("qkv", "o", "gate_up", "down"):
+            G = z[f"l{li}_{n}_q4"].shape[1]
+            lp[n] = {"q4": dev(quant.split_half_to_seq(z[f"l{li}_{n}_q4"])),
+                     "s": dev(z[f"l{li}_{n}_s"].view(bf16).reshape(-1, G)),
+                     "b": dev(z[f"l{li}_{n}_b"].view(bf16).reshape(-1, G))}
+        layers.append(lp)
+    params = {"embed": dev(z["embed"].view(bf16)), "layers": layers, "norm": dev(z["norm"].view(bf16)),
+              "lm_head": dev(z["lm_head"].view(bf16))}
+    cache = {"k": [dev(z[f"k_in{li}"].view(bf16)) for li in range(2)],
+             "v": [dev(z[f"v_in{li}"].view(bf16)) for li in range(2)]}
+    dec = p.qwen3.Decoder(params, cache, cfg, max_batch=2)
+    logits = dec.step(dev(z["tokens"][:, 0].astype(np.int32)), torch.tensor([int(z["ctx"])], dtype=torch.int32, device="cuda"))
+    torch.cuda.synchronize()
+    want = z["logits"]
+    assert dense.max_abs_over_rms(host(logits), want) <= 6e-2
+    assert np.array_equal(host(logits).argmax(-1), want.argmax(-1))
+    for li in range(2):
+        assert rel_rms_err(host(cache["k"][li]).astype(np.float32), z[f"k_out{li}"].view(bf16).astype(np.float32)) <= 8e-2
+
+
+def test_graph_replay_is_deterministic():
+    cfg = inputs.decoder_config(layers=2, hidden=128, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=512)
+    import torch
+    p = pkg()
+    params, cache, tokens = inputs.config5(cfg, 4, 10, max_len=16)
+    dec = p.qwen3.Decoder(dev_params(params), {k: [dev(a) for a in v] for k, v in cache.items()}, cfg, max_batch=4)
+    tok = dev(tokens.astype(np.int32))
+    pos = torch.tensor([10], dtype=torch.int32, device="cuda")
+    out = torch.empty((4, 512), device="cuda")
+    a = dec.step(tok, pos, out).clone()
+    b = dec.step(tok, pos, out).clone()   # replay of the captured graph
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)

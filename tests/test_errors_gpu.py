@@ -1,0 +1,56 @@
+"""Status codes and the sticky-error model on a real device
+(≙ tests/test_gpu_errors.py:21-65 of the reference: an injected failure
+surfaces, stays sticky, and nothing hangs).  Failures are made on the host;
+no kernel is ever made to fault."""
+import numpy as np
+import pytest
+
+from util import dev, pkg
+
+pytestmark = pytest.mark.gpu
+
+
+def test_injected_launch_failure_is_sticky():
+    import torch
+    p = pkg()
+    ctx = p.Context(0)
+    x = torch.randn(4, 64, device="cuda")
+    p.rows.softmax(x, ctx=ctx)
+    assert ctx.error() == 0
+    before = ctx.launch_count
+    ctx.fail_launch_after(2)
+    p.rows.softmax(x, ctx=ctx)                       # launch 1 passes
+    with pytest.raises(p.B200Error) as e:            # launch 2 is refused before it is enqueued
+        p.rows.softmax(x, ctx=ctx)
+    assert e.value.status == p._lib.INTERNAL and "injected" in str(e.value)
+    assert ctx.launch_count == before + 1
+    with pytest.raises(p.B200Error) as e2:           # sticky: every later call returns it
+        p.rows.softmax(x, ctx=ctx)
+    assert e2.value.status == p._lib.INTERNAL
+    assert ctx.error() == p._lib.INTERNAL
+    torch.cuda.synchronize()                         # the device itself is fine
+    fresh = p.Context(0)
+    y = p.rows.softmax(x, ctx=fresh)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all() and fresh.error() == 0
+
+
+def test_invalid_arguments_do_not_poison_the_context():
+    import torch
+    p = pkg()
+    ctx = p.Context(0)
+    x = torch.randn(4, 64, device="cuda")
+    with pytest.raises(p.B200Error) as e:
+        p.rows.rownorm(9, x, ctx=ctx)
+    assert e.value.status == p._lib.INVALID_ARGUMENT
+    assert ctx.error() == 0
+    p.rows.softmax(x, ctx=ctx)
+    torch.cuda.synchronize()
+    assert ctx.error() == 0
+
+
+def test_bad_device_ordinal():
+    p = pkg()
+    with pytest.raises(p.B200Error) as e:
+        p.Context(1000)
+    assert e.value.status == p._lib.INVALID_ARGUMENT

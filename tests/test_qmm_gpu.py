@@ -1,0 +1,181 @@
+"""Weight-only quantised matmul on the device against the oracle: dequantised
+tiles and nibble unpacking bit-exact, products within 2e-2 x RMS (bf16), the
+device quantisers bit-exact, the reference-format fixture, edge cases."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import inputs, quant
+from util import bf16, dev, host, pkg, rel_rms_err
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2  # max-abs error over RMS of the reference output, bf16 outputs
+
+
+def _w4(packed, s, b):
+    return {"q4": dev(packed), "s": dev(s), "b": dev(b)}
+
+
+@pytest.mark.parametrize("n,k", [(64, 256), (48, 4096), (33, 64)])
+def test_int4_dequant_bit_exact(n, k):
+    import torch
+    p = pkg()
+    _, packed, s, b, _ = inputs.config4(1, k, n)
+    want = quant.dequant_f32(quant.bl_unpack_int4(packed), s, b)
+    got = host(p.qwen3.dequantize(_w4(packed, s, b), torch.float32))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    got16 = host(p.qwen3.dequantize(_w4(packed, s, b), torch.bfloat16))
+    assert np.array_equal(got16.view(np.uint16), want.astype(bf16).view(np.uint16))
+
+
+def test_int4_split_half_dequant_bit_exact(golden_dir):
+    import torch
+    p = pkg()
+    z = np.load(os.path.join(golden_dir, "quant_ref.npz"))
+    G = z["p4"].shape[1]
+    s, b = z["s4"].astype(bf16).reshape(-1, G), z["b4"].astype(bf16).reshape(-1, G)
+    w = {"q4h": dev(z["p4"]), "s": dev(s), "b": dev(b)}
+    q = quant.ref_unpack_int4(z["p4"]).reshape(z["p4"].shape[0], -1)
+    got = host(p.qwen3.dequantize(w, torch.float32))
+    assert np.array_equal(got.view(np.uint32), quant.dequant_f32(q, s, b).view(np.uint32))
+
+
+@pytest.mark.parametrize("group", [None, 64])
+def test_int8_dequant_bit_exact(group):
+    import torch
+    p = pkg()
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((40, 512), dtype=np.float32) * 0.02).astype(np.float32)
+    q, s = quant.bl_quantize_int8(w, group)
+    got = host(p.qwen3.dequantize({"q": dev(q), "s": dev(s)}, torch.float32))
+    assert np.array_equal(got.view(np.uint32), quant.dequant_f32(q, s, None).view(np.uint32))
+
+
+def test_device_quantisers_bit_exact():
+    p = pkg()
+    rng = np.random.default_rng(6)
+    w = (rng.standard_normal((96, 1024), dtype=np.float32) * 0.02).astype(np.float32)
+    w[3, 64:128] = 0.0
+    packed, s, b = quant.bl_quantize_int4(w)
+    d = p.qwen3.quantize_int4(dev(w))
+    assert np.array_equal(host(d["q4"]).view(np.uint32), packed)
+    assert np.array_equal(host(d["s"]).view(np.uint16), s.view(np.uint16))
+    assert np.array_equal(host(d["b"]).view(np.uint16), b.view(np.uint16))
+    for group in (None, 64):
+        q, s8 = quant.bl_quantize_int8(w, group)
+        d8 = p.qwen3.quantize_int8(dev(w), group)
+        assert np.array_equal(host(d8["q"]), q)
+        assert np.array_equal(host(d8["s"]).view(np.uint16), s8.view(np.uint16))
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("k,n", [(1024, 512), (4096, 1024)])
+def test_int4_product(m, k, n):
+    p = pkg()
+    x, packed, s, b, _ = inputs.config4(m, k, n)
+    want = quant.qmm(x, quant.bl_unpack_int4(packed), s, b, np.float32)
+    got = host(p.qwen3.linear(dev(x), _w4(packed, s, b))).astype(np.float32)
+    assert rel_rms_err(got, want) <= TOL
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (8, 4096, 12288), (32, 12288, 4096), (1, 12288, 4096),
+                                   (32, 4096, 1024)])
+def test_int4_product_qwen3_shapes(m, k, n):
+    """Full Qwen3-8B projection shapes.  The CPU side checks a sample of the
+    outputs (512 columns) so the suite stays fast."""
+    p = pkg()
+    x, packed, s, b, _ = inputs.config4(m, k, n)
+    got = host(p.qwen3.linear(dev(x), _w4(packed, s, b))).astype(np.float32)
+    cols = np.random.default_rng(0).choice(n, 512, replace=False)
+    want = quant.qmm(x, quant.bl_unpack_int4(packed[cols]), s[cols], b[cols], np.float32)
+    assert rel_rms_err(got[:, cols], want) <= TOL
+    assert np.isfinite(got).all()
+
+
+def test_int4_one_hot_rows_return_the_dequantised_column():
+    """Size-independent property: with x = e_k the product is column k of the
+    dequantised matrix (to bf16 rounding)."""
+    p = pkg()
+    k, n = 4096, 2048
+    _, packed, s, b, _ = inputs.config4(1, k, n)
+    ks = [0, 7, 63, 64, 1000, 4095]
+    x = np.zeros((len(ks), k), np.float32)
+    for i, kk in enumerate(ks):
+        x[i, kk] = 1.0
+    got = host(p.qwen3.linear(dev(x.astype(bf16)), _w4(packed, s, b))).astype(np.float32)
+    wd = quant.dequant_f32(quant.bl_unpack_int4(packed), s, b)
+    want = wd[:, ks].T
+    ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want), 1e-30))) - 7)
+    assert np.all(np.abs(got - want) <= 0.51 * ulp + 1e-6)
+
+
+def test_reference_format_against_fixture(golden_dir):
+    """The reference's own int4 format (split-half bytes, MLX-style grid, possibly
+    negative scale) and its _matvec_int4 output recorded from the reference."""
+    p = pkg()
+    z = np.load(os.path.join(golden_dir, "quant_ref.npz"))
+    G = z["p4"].shape[1]
+    # K = 256 here; pad nothing: the kernel takes any multiple of 64
+    w = {"q4h": dev(z["p4"]), "s": dev(z["s4"].astype(bf16).reshape(-1, G)), "b": dev(z["b4"].astype(bf16).reshape(-1, G))}
+    x = z["x"].view(bf16)
+    got = host(p.qwen3.linear(dev(x), w)).astype(np.float32)
+    want = z["mv4"].view(bf16).astype(np.float32)
+    assert rel_rms_err(got, want) <= TOL
+    # and the same values through the sequential layout
+    seq = quant.split_half_to_seq(z["p4"])
+    got2 = host(p.qwen3.linear(dev(x), {"q4": dev(seq), "s": w["s"], "b": w["b"]})).astype(np.float32)
+    assert rel_rms_err(got2, want) <= TOL and rel_rms_err(got2, got) <= 1e-2  # same values, other k order
+    # int8, group-wise (the reference's), against its _matvec_int8
+    w8 = {"q": dev(z["q8"].reshape(z["q8"].shape[0], -1)), "s": dev(z["s8"].astype(bf16).reshape(-1, G))}
+    got8 = host(p.qwen3.linear(dev(x), w8)).astype(np.float32)
+    assert rel_rms_err(got8, z["mv8"].view(bf16).astype(np.float32)) <= TOL
+
+
+@pytest.mark.parametrize("m", [1, 8, 32])
+@pytest.mark.parametrize("k,n", [(4096, 1024), (1024, 4096)])
+def test_int8_per_channel_product(m, k, n):
+    p = pkg()
+    x, q, s, _ = inputs.config3(m, k, n)
+    want = quant.qmm(x, q, s, None, np.float32)
+    got = host(p.qwen3.linear(dev(x), {"q": dev(q), "s": dev(s)})).astype(np.float32)
+    assert rel_rms_err(got, want) <= TOL
+
+
+@pytest.mark.parametrize("m", [1, 5, 32])
+def test_bf16_weights_product(m):
+    """bits = 16: the LM-head form (bf16 [out, in] matrix), f32 logits holding bf16-rounded values."""
+    p = pkg()
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((1000, 512), dtype=np.float32) * 0.02).astype(bf16)
+    x = rng.standard_normal((m, 512), dtype=np.float32).astype(bf16)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    got = host(p.qwen3.linear(dev(x), dev(w), out_f32=True))
+    assert got.dtype == np.float32 and rel_rms_err(got, want) <= TOL
+    assert np.array_equal(got, got.astype(bf16).astype(np.float32))  # values are bf16-representable
+
+
+def test_edge_cases():
+    import torch
+    p = pkg()
+    # ragged N (not a multiple of 16), smallest K, strided x, residual epilogue
+    x, packed, s, b, _ = inputs.config4(3, 64, 37)
+    want = quant.qmm(x, quant.bl_unpack_int4(packed), s, b, np.float32)
+    w = _w4(packed, s, b)
+    assert rel_rms_err(host(p.qwen3.linear(dev(x), w)).astype(np.float32), want) <= TOL
+    xs = torch.zeros((3, 200), dtype=torch.bfloat16, device="cuda")
+    xs[:, :64] = dev(x)
+    assert np.array_equal(host(p.qwen3.linear(xs[:, :64], w)).view(np.uint16), host(p.qwen3.linear(dev(x), w)).view(np.uint16))
+    res = np.random.default_rng(1).standard_normal((3, 37), dtype=np.float32).astype(bf16)
+    got = host(p.qwen3.linear(dev(x), w, residual=dev(res))).astype(np.float32)
+    want_r = (res.astype(np.float32) + want.astype(bf16).astype(np.float32)).astype(bf16).astype(np.float32)
+    assert rel_rms_err(got, want_r) <= TOL
+    # empty problems launch nothing
+    n0 = p.default_context().launch_count
+    out = p.qwen3.linear(dev(x)[:0], w)
+    assert out.shape == (0, 37) and p.default_context().launch_count == n0
+    # too many rows: refused, not wrong
+    with pytest.raises(p.B200Error) as e:
+        p.qwen3.linear(torch.zeros((33, 64), dtype=torch.bfloat16, device="cuda"), w)
+    assert e.value.status == p._lib.UNIMPLEMENTED
+    assert p.default_context().error() == 0
