@@ -74,6 +74,7 @@ struct b200_decoder {
                 *act = nullptr;
   float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr;
   bool use_graph = true;
+  cudaStream_t capture_stream = nullptr;  // graphs are captured here (the caller's stream may be the legacy one)
   std::map<std::tuple<int, const void*, const void*, const void*>, cudaGraphExec_t> graphs;
   std::map<int, int64_t> launches;
 };
@@ -222,6 +223,7 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
     e = cudaMalloc(reinterpret_cast<void**>(&d->attn_scratch),
                    b200_attention_scratch_bytes(c.max_batch, c.heads, c.head_dim, c.max_len));
   if (e == cudaSuccess && tp != nullptr && tp->world > 1) e = Alloc(&d->logits_local, B * c.vocab);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) {
     s = Fail(B200_RESOURCE_EXHAUSTED, "b200_decoder_create: %s", cudaGetErrorString(e));
     b200_decoder_destroy(d);
@@ -235,6 +237,7 @@ void b200_decoder_destroy(b200_decoder* d) {
   if (d == nullptr) return;
   cudaSetDevice(d->ctx->device);
   for (auto& kv : d->graphs) cudaGraphExecDestroy(kv.second);
+  if (d->capture_stream != nullptr) cudaStreamDestroy(d->capture_stream);
   for (void* p : {static_cast<void*>(d->x), static_cast<void*>(d->h), static_cast<void*>(d->qkv),
                   static_cast<void*>(d->q), static_cast<void*>(d->attn), static_cast<void*>(d->gu),
                   static_cast<void*>(d->act), static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
@@ -263,13 +266,14 @@ b200_status b200_decoder_step(b200_decoder* d, b200_stream stream, const int32_t
                                    static_cast<const void*>(logits));
   auto it = d->graphs.find(key);
   if (it == d->graphs.end()) {
-    cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    cudaStream_t cs = d->capture_stream;
+    cudaError_t e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
     if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaStreamBeginCapture: %s", cudaGetErrorString(e)));
     const int64_t before = d->ctx->launches.load();
-    s = Enqueue(d, stream, tokens, pos, logits, batch);
+    s = Enqueue(d, cs, tokens, pos, logits, batch);
     const int64_t count = d->ctx->launches.load() - before;
     cudaGraph_t graph = nullptr;
-    e = cudaStreamEndCapture(stream, &graph);
+    e = cudaStreamEndCapture(cs, &graph);
     if (s != B200_OK) {
       if (graph != nullptr) cudaGraphDestroy(graph);
       return s;

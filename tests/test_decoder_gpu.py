@@ -50,7 +50,8 @@ def test_pieces_against_oracle(B, H, KV, D, S, pos):
     kd, vd = dev(kc), dev(vc)
     qo = torch.empty((B, H, D), dtype=torch.bfloat16, device="cuda")
     posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
-    _call(p, L.b200_qk_norm_rope_cache, dev(qkv).data_ptr(), dev(qn).data_ptr(), dev(kn).data_ptr(), qo.data_ptr(),
+    qkvd, qnd, knd = dev(qkv), dev(qn), dev(kn)   # keep the device buffers alive across the launch
+    _call(p, L.b200_qk_norm_rope_cache, qkvd.data_ptr(), qnd.data_ptr(), knd.data_ptr(), qo.data_ptr(),
           kd.data_ptr(), vd.data_ptr(), posd.data_ptr(), B, H, KV, D, S, 1e6, 1e-6)
     from oracle.rownorm import rms_norm
     positions = np.full((B,), pos)
@@ -84,7 +85,8 @@ def test_silu_mul_and_embed():
     rng = np.random.default_rng(12)
     gu = (rng.standard_normal((5, 2 * 384), dtype=np.float32) * 2).astype(bf16)
     out = torch.empty((5, 384), dtype=torch.bfloat16, device="cuda")
-    _call(p, L.b200_silu_mul, dev(gu).data_ptr(), out.data_ptr(), 5, 384)
+    gud = dev(gu)
+    _call(p, L.b200_silu_mul, gud.data_ptr(), out.data_ptr(), 5, 384)
     want = odec.silu_mul(gu[:, :384], gu[:, 384:])
     got = host(out)
     ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want.astype(np.float32)), 1e-30))) - 7)
@@ -92,7 +94,8 @@ def test_silu_mul_and_embed():
     table = rng.standard_normal((100, 256), dtype=np.float32).astype(bf16)
     tok = np.array([3, 99, 0, 3], np.int32)
     e = torch.empty((4, 256), dtype=torch.bfloat16, device="cuda")
-    _call(p, L.b200_embed, dev(table).data_ptr(), dev(tok).data_ptr(), e.data_ptr(), 4, 256)
+    tabled, tokd = dev(table), dev(tok)
+    _call(p, L.b200_embed, tabled.data_ptr(), tokd.data_ptr(), e.data_ptr(), 4, 256)
     assert np.array_equal(host(e).view(np.uint16), table[tok].view(np.uint16))
 
 
