@@ -1,0 +1,384 @@
+"""Benchmark of the decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+A step is one decode step (one new token per sequence) of the Qwen3-8B-shaped
+int4-g64 decoder at position 2048 over a 2048-token bf16 KV cache, with
+random-init weights (synthetic; no checkpoint, no dataset).  Rank 0 prints ONE
+JSON line:
+  value     tokens/s with tokens and weights resident in HBM (device-timed,
+            CUDA events on the launching stream, max over ranks);
+  e2e       the same through the public call with pinned-host tokens copied in
+            and the logits copied out every step;
+  roofline  the dominant kernel (int4 dequant-GEMV): the step's 4 x layers
+            projection launches replayed back to back over their own distinct
+            weight buffers, algorithmic bytes / mean launch time / measured HBM peak;
+  cpu_baseline  the C restatement of the reference's decode math (oracle/)
+            on this host's cores, on a bounded sample scaled to a full step.
+--impl reference times only that CPU restatement (the reference's own
+kernels are Metal and cannot run here).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, inter=12288, vocab=151936,
+           theta=1e6, eps=1e-6)
+CTX = 2048            # prior tokens in the cache; the step runs at pos = CTX
+MAX_LEN = 2176        # cache slots allocated (the window rounded up, like generate.py:136-144)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def step_bytes(cfg, batch, world=1):
+    """Algorithmic bytes one decode step must read, whole job (all ranks)."""
+    E, H, KV, D, I, V, L = (cfg[k] for k in ("hidden", "heads", "kv_heads", "head_dim", "inter", "vocab", "layers"))
+    params = L * ((H + 2 * KV) * D * E + E * H * D + 2 * I * E + E * I)
+    w = params * 0.5625                      # 4 bits + bf16 scale and offset per 64
+    head = V * E * 2
+    kv = L * batch * 2 * KV * (CTX + 1) * D * 2
+    return w + head + kv
+
+
+class Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, f"/tmp/b200_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return res
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            res = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        return res
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline: the C restatement of the reference's decode math, on a bounded sample
+# ------------------------------------------------------------------------------------------
+
+def host_sample_params(cfg, run_layers, run_vocab, seed=4):
+    """Host-side weights for the sample: random nibbles and plausible scales
+    (timing does not depend on their values)."""
+    import ml_dtypes
+    bf16 = ml_dtypes.bfloat16
+    rng = np.random.default_rng(seed)
+    E, H, KV, D, I = cfg["hidden"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"]
+
+    def qmat(n, k):
+        return {"q4": rng.integers(0, 2 ** 32, size=(n, k // 8), dtype=np.uint32),
+                "s": np.full((n, k // 64), 0.008, bf16), "b": np.full((n, k // 64), -0.06, bf16)}
+    layers = []
+    for _ in range(run_layers):
+        layers.append({"attn_norm": np.ones(E, bf16), "qkv": qmat((H + 2 * KV) * D, E), "q_norm": np.ones(D, bf16),
+                       "k_norm": np.ones(D, bf16), "o": qmat(E, H * D), "mlp_norm": np.ones(E, bf16),
+                       "gate_up": qmat(2 * I, E), "down": qmat(E, I)})
+    embed = (rng.standard_normal((4096, E), dtype=np.float32) * 0.02).astype(bf16)
+    head = (rng.standard_normal((run_vocab, E), dtype=np.float32) * 0.02).astype(bf16)
+    return {"embed": embed, "layers": layers, "norm": np.ones(E, bf16), "lm_head": head}
+
+
+def cpu_baseline(cfg, batch, steps=1, warmup=0, run_layers=2, run_vocab=8192):
+    """tokens/s of the CPU restatement, from `run_layers` layers and `run_vocab`
+    LM-head rows scaled linearly to the full step."""
+    import ml_dtypes
+    from oracle import cpu_ref
+    bf16 = ml_dtypes.bfloat16
+    sub = dict(cfg, layers=run_layers)
+    params = host_sample_params(cfg, run_layers, run_vocab)
+    rng = np.random.default_rng(5)
+    cache = {"k": [rng.standard_normal((batch, cfg["kv_heads"], MAX_LEN, cfg["head_dim"]), dtype=np.float32).astype(bf16)
+                   for _ in range(run_layers)],
+             "v": [rng.standard_normal((batch, cfg["kv_heads"], cfg["head_dim"], MAX_LEN), dtype=np.float32).astype(bf16)
+                   for _ in range(run_layers)]}
+    tokens = rng.integers(0, 4096, size=(batch,)).astype(np.int32)
+    times_layers, times_head = [], []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        cpu_ref.decode_step(params, tokens, cache, CTX, sub, run_layers=run_layers, run_vocab=16)
+        t1 = time.perf_counter()
+        cpu_ref.decode_step(params, tokens, cache, CTX, sub, run_layers=0, run_vocab=run_vocab)
+        t2 = time.perf_counter()
+        if it >= warmup:
+            times_layers.append(t1 - t0)
+            times_head.append(t2 - t1)
+    t_step = float(np.median(times_layers)) * cfg["layers"] / run_layers + \
+        float(np.median(times_head)) * cfg["vocab"] / run_vocab
+    return {"value": batch / t_step, "unit": "tok/s", "cores": cpu_ref.threads(), "kind": "port",
+            "sample": f"{run_layers} of {cfg['layers']} layers + {run_vocab} of {cfg['vocab']} LM-head rows per step, "
+                      f"scaled linearly; C/OpenMP restatement of qwen3.py forward (oracle/cpu_ref.c)",
+            "ms_per_step_scaled": t_step * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    cb = cpu_baseline(CFG, args.batch, steps=args.steps, warmup=min(args.warmup, 1))
+    line = {"impl": "reference", "metric": "decode_tok_s", "value": cb["value"], "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": cb["ms_per_step_scaled"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int4 weights, bf16 activations, f32 accumulate", "data": "synthetic",
+            "config": workload_config(args.batch, 1), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": time.perf_counter() - t0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(batch, world):
+    return {"workload": "configs[4]: Qwen3-8B-shape int4-g64 decode step (36 layers, hidden 4096, 32q/8kv heads x 128, "
+                        "inter 12288, vocab 151936 untied bf16 LM head), 2048-token bf16 KV cache, pos 2048",
+            "batch": batch, "parallelism": f"tp{world}" if world > 1 else "single",
+            "l2": "inputs larger than L2: every step streams >= 5.4 GB of distinct weights"}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+
+def build_device_model(pkg, cfg_local, batch, device, seed, world, rank):
+    """Random-init N(0, 0.02) weights quantised on the device (int4-g64), norms
+    gain 1, bf16 embedding / LM head, cache of CTX prior tokens ~ N(0, 1)."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed * 1000 + rank)
+    E, H, KV, D, I, V = (cfg_local[k] for k in ("hidden", "heads", "kv_heads", "head_dim", "inter", "vocab"))
+
+    def qmat(n, k):
+        w = torch.randn((n, k), generator=g, device=device, dtype=torch.float32).mul_(0.02)
+        q = pkg.qwen3.quantize_int4(w)
+        del w
+        return q
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    layers = []
+    for _ in range(cfg_local["layers"]):
+        layers.append({"attn_norm": ones(E), "qkv": qmat((H + 2 * KV) * D, E), "q_norm": ones(D), "k_norm": ones(D),
+                       "o": qmat(E, H * D), "mlp_norm": ones(E), "gate_up": qmat(2 * I, E), "down": qmat(E, I)})
+    gfull = torch.Generator(device=device)
+    gfull.manual_seed(seed * 1000 + 999)   # the embedding is replicated: same on every rank
+    vocab_full = V * world
+    embed = torch.randn((vocab_full, E), generator=gfull, device=device, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
+    head = torch.randn((V, E), generator=g, device=device, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
+    params = {"embed": embed, "layers": layers, "norm": ones(E), "lm_head": head}
+    cache = pkg.qwen3.init_cache(cfg_local, batch, MAX_LEN, device)
+    for li in range(cfg_local["layers"]):
+        cache["k"][li][:, :, :CTX] = torch.randn((batch, KV, CTX, D), generator=g, device=device).to(torch.bfloat16)
+        cache["v"][li][:, :, :, :CTX] = torch.randn((batch, KV, D, CTX), generator=g, device=device).to(torch.bfloat16)
+    torch.cuda.synchronize()
+    return params, cache
+
+
+def time_projection_kernels(pkg, params, cfg_local, batch, device, reps):
+    """The dequant-GEMV alone: every int4 projection of the model launched back
+    to back over its own weights (4 x layers distinct buffers, far beyond L2)."""
+    import torch
+    E, H, KV, D, I = (cfg_local[k] for k in ("hidden", "heads", "kv_heads", "head_dim", "inter"))
+    xs = {E: torch.randn((batch, E), device=device).to(torch.bfloat16),
+          H * D: torch.randn((batch, H * D), device=device).to(torch.bfloat16),
+          I: torch.randn((batch, I), device=device).to(torch.bfloat16)}
+    jobs, nbytes = [], 0
+    for lp in params["layers"]:
+        for name in ("qkv", "o", "gate_up", "down"):
+            w = lp[name]
+            n, k = w["q4"].shape[0], w["q4"].shape[1] * 8
+            jobs.append((xs[k], w))
+            nbytes += n * k * 0.5625 + 2 * batch * (k + n)
+    for x, w in jobs[:8]:
+        pkg.qwen3.linear(x, w)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        for x, w in jobs:
+            pkg.qwen3.linear(x, w)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    launches = reps * len(jobs)
+    return nbytes / len(jobs), ms * 1e-3 / launches, launches
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(device))
+    ctx = pkg.default_context(local)
+    tp = None
+    cfg_local = dict(CFG)
+    if world > 1:
+        from metal_pjrt_plugin_b200 import parallel
+        tp = parallel.TensorParallel.from_torch_distributed(ctx)
+        cfg_local = parallel.local_config(CFG, world)
+    B = args.batch
+    params, cache = build_device_model(pkg, cfg_local, B, device, 4, world, rank)
+    dec = pkg.qwen3.Decoder(params, cache, cfg_local, max_batch=B, ctx=ctx, tp=tp)
+
+    tok_host = torch.randint(0, CFG["vocab"], (B,), dtype=torch.int32).pin_memory()
+    tok = tok_host.to(device)
+    pos = torch.tensor([CTX], dtype=torch.int32, device=device)
+    logits = torch.empty((B, CFG["vocab"]) if world == 1 else (world, B, cfg_local["vocab"]), dtype=torch.float32,
+                         device=device)
+    logits_host = torch.empty(logits.shape, dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(seconds):
+        if world == 1:
+            return seconds
+        t = torch.tensor([seconds], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing -------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        dec.step(tok, pos, logits)
+    barrier()
+    clocks = Clocks(local)
+    if rank == 0:
+        clocks.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record(stream)
+    for _ in range(args.steps):
+        dec.step(tok, pos, logits)
+    stop.record(stream)
+    barrier()
+    t_dev = max_over_ranks(start.elapsed_time(stop) * 1e-3)
+
+    # ---- end to end: pinned tokens in, logits out, every step --------------------
+    for _ in range(2):
+        tok.copy_(tok_host, non_blocking=True)
+        dec.step(tok, pos, logits)
+        logits_host.copy_(logits, non_blocking=True)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok.copy_(tok_host, non_blocking=True)
+        dec.step(tok, pos, logits)
+        logits_host.copy_(logits, non_blocking=True)
+        torch.cuda.synchronize()   # the caller reads the logits before the next step
+    t_e2e = max_over_ranks(time.perf_counter() - t0)
+    clk = clocks.stop() if rank == 0 else None
+    err = ctx.error()
+
+    # ---- the dominant kernel alone ----------------------------------------------
+    peak, peak_kind = measured_peaks()
+    bytes_per_launch, sec_per_launch, qlaunches = time_projection_kernels(pkg, params, cfg_local, B, device, reps=3)
+    achieved = bytes_per_launch / sec_per_launch / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    cb = cpu_baseline(CFG, B, steps=1, warmup=0) if world == 1 else None
+    total_bytes = step_bytes(CFG, B, world)
+    line = {
+        "metric": "decode_tok_s", "value": B * args.steps / t_dev, "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t_dev * 1e3 / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights, bf16 activations, f32 accumulate", "data": "synthetic",
+        "config": workload_config(B, world),
+        "e2e": {"value": B * args.steps / t_e2e, "unit": "tok/s", "h2d_bytes_per_step": int(tok_host.numel() * 4),
+                "d2h_bytes_per_step": int(logits_host.numel() * 4)},
+        "gpu_launches": int(dec.launches_per_step(B) * args.steps),
+        "launches_per_step": int(dec.launches_per_step(B)),
+        "step_hbm": {"algorithmic_gb_per_step": total_bytes / 1e9,
+                     "achieved_gbs_per_gpu": total_bytes / world / (t_dev / args.steps) / 1e9,
+                     "frac_of_peak": total_bytes / world / (t_dev / args.steps) / 1e9 / peak},
+        "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (int4-g64 dequant-GEMV, all 4 x layers projections)",
+                     "achieved": achieved, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s",
+                     "frac": achieved / peak, "frac_of_nominal_8tbs": achieved / 8000.0,
+                     "algorithmic_bytes_per_launch": bytes_per_launch, "us_per_launch": sec_per_launch * 1e6,
+                     "launches_timed": qlaunches, "traffic": None},
+        "clocks": clk, "device_status": err,
+    }
+    if cb is not None:
+        line["cpu_baseline"] = cb
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,166 @@
+"""Per-operator micro-benchmarks (the method of the reference's
+bench/gemm_bench.cc:7-16,102-124 and bench/jax_bench.py: back-to-back launches
+cycling through distinct weight buffers so nothing stays in L2; CUDA-event
+time; JSON lines).  Also the small cases the ncu summaries under profiles/ come from.
+
+    python metal-pjrt-plugin_b200/opbench.py qmm  --bits 4 --m 1 --n 4096 --k 4096 [--buffers 32] [--reps 5]
+    python metal-pjrt-plugin_b200/opbench.py gemm --m 2048 --n 4096 --k 4096 [--act 3] [--bias]
+    python metal-pjrt-plugin_b200/opbench.py rows --kind softmax --rows 8192 --n 1024 [--dtype f32]
+    python metal-pjrt-plugin_b200/opbench.py sweep          # the benchmark configs 2-4
+"""
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402
+
+HBM_NOMINAL = 8000.0
+BF16_NOMINAL = 2250.0
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def timed(fn, reps, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e-3 / reps
+
+
+def bench_qmm(pkg, bits, m, n, k, buffers, reps, group=64):
+    import torch
+    dev = "cuda"
+    ws = []
+    for i in range(buffers):
+        if bits == 4:
+            ws.append({"q4": torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int32, device=dev),
+                       "s": torch.full((n, k // 64), 0.008, dtype=torch.bfloat16, device=dev),
+                       "b": torch.full((n, k // 64), -0.06, dtype=torch.bfloat16, device=dev)})
+        elif bits == 8:
+            g = k if group == 0 else group
+            ws.append({"q": torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev),
+                       "s": torch.full((n, k // g), 0.001, dtype=torch.bfloat16, device=dev)})
+        else:
+            ws.append(torch.randn((n, k), device=dev).mul_(0.02).to(torch.bfloat16))
+    x = torch.randn((m, k), device=dev).to(torch.bfloat16)
+
+    def run():
+        for w in ws:
+            pkg.qwen3.linear(x, w)
+    sec = timed(run, reps) / buffers
+    if bits == 4:
+        nbytes = n * k * 0.5625
+    elif bits == 8:
+        nbytes = n * k + 2 * n * (k // (k if group == 0 else group))
+    else:
+        nbytes = n * k * 2
+    nbytes += 2 * m * (k + n)
+    hbm, _, kind = peaks()
+    gbs = nbytes / sec / 1e9
+    plan = pkg.qwen3.qmm_plan(m, n, k, bits, 64 if bits == 4 else (k if group == 0 else group))
+    return {"op": "qmm", "bits": bits, "m": m, "n": n, "k": k, "buffers": buffers, "us": sec * 1e6,
+            "algorithmic_bytes": nbytes, "gbs": gbs, f"frac_of_{kind}": gbs / hbm, "frac_of_nominal": gbs / HBM_NOMINAL,
+            "rows_per_cta": plan[0], "split_k": plan[1]}
+
+
+def bench_gemm(pkg, m, n, k, act, bias, reps, dtype="bf16", transpose_b=False, buffers=4):
+    import torch
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    dev = "cuda"
+    As = [torch.randn((m, k), device=dev).to(dt) for _ in range(buffers)]
+    Bs = [torch.randn((n, k) if transpose_b else (k, n), device=dev).mul_(0.02).to(dt) for _ in range(buffers)]
+    bias_t = torch.randn((n,), device=dev).mul_(0.01).to(dt) if bias else None
+
+    def run():
+        for a, b in zip(As, Bs):
+            pkg.blas.matmul(a, b, bias=bias_t, act=act, transpose_b=transpose_b)
+    sec = timed(run, reps) / buffers
+    es = 4 if dtype == "f32" else 2
+    flops = 2.0 * m * n * k
+    nbytes = es * (m * k + k * n + m * n) + (es * n if bias else 0)
+    hbm, tf, kind = peaks()
+    B = pkg.blas
+    d = torch.empty((m, n), dtype=dt, device=dev)
+    route = B.gemm_route(B.GemmParams(m, n, k, B.Operand(As[0], k), B.Operand(Bs[0], Bs[0].stride(0), transpose=transpose_b),
+                                      B.Operand(d, n)))
+    return {"op": "gemm", "dtype": dtype, "m": m, "n": n, "k": k, "act": act, "bias": bool(bias), "route": route,
+            "us": sec * 1e6, "tflops": flops / sec / 1e12, f"frac_of_{kind}_tensor": flops / sec / 1e12 / tf,
+            "frac_of_nominal_tensor": flops / sec / 1e12 / BF16_NOMINAL, "gbs": nbytes / sec / 1e9,
+            f"frac_of_{kind}_hbm": nbytes / sec / 1e9 / hbm}
+
+
+def bench_rows(pkg, kind, rows, n, dtype, reps, buffers=4):
+    import torch
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    xs = [torch.randn((rows, n), device="cuda").mul_(3.0).to(dt) for _ in range(buffers)]
+    ys = [torch.empty_like(x) for x in xs]
+    gain = torch.ones((n,), device="cuda").to(dt)
+    code = {"rms": 0, "softmax": 1, "log_softmax": 2, "layernorm": 3}[kind]
+
+    def run():
+        for x, y in zip(xs, ys):
+            pkg.rows.rownorm(code, x, gain=gain if code in (0, 3) else None, eps=1e-6, out=y)
+    sec = timed(run, reps) / buffers
+    nbytes = 2 * rows * n * xs[0].element_size()
+    hbm, _, k = peaks()
+    return {"op": "rows", "kind": kind, "rows": rows, "n": n, "dtype": dtype, "us": sec * 1e6,
+            "gbs": nbytes / sec / 1e9, f"frac_of_{k}": nbytes / sec / 1e9 / hbm}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["qmm", "gemm", "rows", "sweep"])
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--group", type=int, default=64, help="int8: 64, or 0 for per-channel")
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--buffers", type=int, default=32)
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--act", type=int, default=0)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--tb", action="store_true")
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--kind", default="softmax")
+    ap.add_argument("--rows", type=int, default=8192)
+    a = ap.parse_args()
+    pkg = load_package()
+    if a.op == "qmm":
+        print(json.dumps(bench_qmm(pkg, a.bits, a.m, a.n, a.k, a.buffers, a.reps, a.group)), flush=True)
+    elif a.op == "gemm":
+        print(json.dumps(bench_gemm(pkg, a.m, a.n, a.k, a.act, a.bias, a.reps, a.dtype, a.tb, min(a.buffers, 4))), flush=True)
+    elif a.op == "rows":
+        print(json.dumps(bench_rows(pkg, a.kind, a.rows, a.n, a.dtype, a.reps)), flush=True)
+    else:
+        shapes = [(4096, 4096), (4096, 1024), (4096, 12288), (12288, 4096)]
+        for bits in (4, 8):
+            for (k, n) in shapes:
+                for m in (1, 8, 32):
+                    buffers = max(8, int(512e6 // (n * k * bits / 8)))
+                    print(json.dumps(bench_qmm(pkg, bits, m, n, k, min(buffers, 64), 3, 64 if bits == 4 else 0)), flush=True)
+        for m in (1, 16, 128, 2048, 8192):
+            print(json.dumps(bench_gemm(pkg, m, 4096, 4096, 3, True, 3)), flush=True)
+        for kind, rows, n, dt in [("softmax", 8192, 1024, "f32"), ("layernorm", 8192, 1024, "f32"),
+                                  ("rms", 8192, 4096, "bf16"), ("softmax", 1024, 2048, "f32"), ("rms", 32, 4096, "bf16")]:
+            print(json.dumps(bench_rows(pkg, kind, rows, n, dt, 5)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

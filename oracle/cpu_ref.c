@@ -78,6 +78,7 @@ void oracle_qmv_int4(const uint16_t* x, const uint32_t* q, const uint16_t* s, co
       for (int m = 0; m < M; ++m) {
         const float* xr = xf + (size_t)m * K + g * 64;
         float t = 0.0f;
+#pragma omp simd reduction(+ : t)
         for (int j = 0; j < 64; ++j) t += xr[j] * qf[j];
         acc[m] += t * sc + xs[m * G + g] * bi;
       }
@@ -102,6 +103,7 @@ void oracle_qmv_int8(const uint16_t* x, const int8_t* q, const uint16_t* s, floa
         const int8_t* qr = q + (size_t)n * K + (size_t)g * group;
         const float* xr = xf + (size_t)m * K + (size_t)g * group;
         float t = 0.0f;
+#pragma omp simd reduction(+ : t)
         for (int j = 0; j < group; ++j) t += xr[j] * (float)qr[j];
         acc += t * bf2f(s[(size_t)n * G + g]);
       }
@@ -120,6 +122,7 @@ void oracle_mv_bf16(const uint16_t* x, const uint16_t* w, float* out, int M, int
     for (int m = 0; m < M; ++m) {
       const float* xr = xf + (size_t)m * K;
       float t = 0.0f;
+#pragma omp simd reduction(+ : t)
       for (int k = 0; k < K; ++k) t += xr[k] * bf2f(wr[k]);
       out[(size_t)m * N + n] = t;
     }
@@ -268,6 +271,7 @@ void oracle_decode_step(const oracle_cfg* c, const oracle_layer* layers, const u
         float m = -INFINITY;
         for (int s = 0; s < nv; ++s) {
           float t = 0.0f;
+#pragma omp simd reduction(+ : t)
           for (int d = 0; d < D; ++d) t += bf2f(qh[d]) * bf2f(kc[(size_t)s * D + d]);
           p[s] = t * scale;
           m = p[s] > m ? p[s] : m;
@@ -277,6 +281,7 @@ void oracle_decode_step(const oracle_cfg* c, const oracle_layer* layers, const u
         for (int s = 0; s < nv; ++s) p[s] /= sum;
         for (int d = 0; d < D; ++d) {
           float t = 0.0f;
+#pragma omp simd reduction(+ : t)
           for (int s = 0; s < nv; ++s) t += p[s] * bf2f(vc[(size_t)d * S + s]);
           att[((size_t)b * H + hh) * D + d] = f2bf(t);
         }
