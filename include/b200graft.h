@@ -131,6 +131,14 @@ typedef enum { B200_QMM_OUT_BF16 = 0,      /* out bf16 [M, ldo] */
                B200_QMM_OUT_F32_RAW = 3    /* out f32 [M, ldo], unrounded (a partial sum of a K-sharded product) */
 } b200_qmm_epilogue;
 
+/* Input transforms fused into the staging of x (each CTA applies them to the
+ * slice of x it reads, so the transformed activations are never written out):
+ *   RMSNORM  x' = bf16(x * rsqrt(mean(x^2) + eps) * gain)  (rms_norm feeding a projection,
+ *            examples/llm/qwen3.py:361-362,374-375); up to 8 rows;
+ *   SILU_MUL x is [M, 2K] = [gate | up]; x' = silu(gate) * up with the reference's
+ *            bf16 roundings (qwen3.py:376). */
+typedef enum { B200_QMM_PRO_NONE = 0, B200_QMM_PRO_RMSNORM = 1, B200_QMM_PRO_SILU_MUL = 2 } b200_qmm_prologue;
+
 typedef struct {
   int32_t bits;          /* 4, 8 or 16 */
   int32_t group;         /* 64, or K (per output channel; int8 only) */
@@ -143,7 +151,10 @@ typedef struct {
   const void* residual;  /* B200_QMM_ADD_RESIDUAL only; may alias out */
   void* out;
   int64_t M, N, K;
-  int64_t ldx, ldo;      /* 0 = dense (K and N) */
+  int64_t ldx, ldo;      /* 0 = dense (K, or 2K under SILU_MUL; and N) */
+  int32_t prologue;      /* b200_qmm_prologue */
+  float eps;             /* RMSNORM */
+  const void* prologue_gain; /* RMSNORM: bf16 [K] */
 } b200_qmm_params;
 
 b200_status b200_qmm_validate(const b200_qmm_params* p);
@@ -243,6 +254,16 @@ size_t b200_attention_scratch_bytes(int64_t batch, int heads, int head_dim, int6
 b200_status b200_attention_decode(b200_context* ctx, b200_stream stream, const void* q, const void* k_cache,
                                   const void* v_cache, void* out, const int32_t* pos, void* scratch,
                                   int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_len);
+/* The fused form the decoder uses: per-head RMSNorm + RoPE of q and of the new k,
+ * the cache writes of k and v at *pos, and attention over slots [0, *pos], all
+ * from the fused projection row qkv bf16 [B, (H + 2 KV) * D] (qwen3.py:363-372).
+ * inv_freq: f32 [D/2] = theta^(-2i/D), or NULL to compute it in the kernel.
+ * A *pos outside [0, max_len) writes nothing and reports B200_INVALID_ARGUMENT
+ * through the context's device status word. */
+b200_status b200_attention_step(b200_context* ctx, b200_stream stream, const void* qkv, const void* q_norm,
+                                const void* k_norm, const float* inv_freq_or_null, void* k_cache, void* v_cache,
+                                void* out, const int32_t* pos, void* scratch, int64_t batch, int heads,
+                                int kv_heads, int head_dim, int64_t max_len, float theta, float eps);
 /* silu(gate) * up with the reference's bf16 roundings (qwen3.py:376). gate_up bf16 [B, 2*inter]. */
 b200_status b200_silu_mul(b200_context* ctx, b200_stream stream, const void* gate_up, void* out,
                           int64_t batch, int64_t inter);

@@ -16,6 +16,7 @@ STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "UNIMPLEMENTED", "INTERNAL", "RESOURCE
 F32, F16, BF16 = 0, 1, 2
 ROUTE_NONE, ROUTE_TCGEN05, ROUTE_FEWROW, ROUTE_SIMT = 0, 1, 2, 3
 QMM_OUT_BF16, QMM_ADD_RESIDUAL, QMM_OUT_F32, QMM_OUT_F32_RAW = 0, 1, 2, 3
+QMM_PRO_NONE, QMM_PRO_RMSNORM, QMM_PRO_SILU_MUL = 0, 1, 2
 KIND_RMS, KIND_SOFTMAX, KIND_LOG_SOFTMAX, KIND_LAYERNORM = 0, 1, 2, 3
 TP_ID_BYTES = 128
 
@@ -45,7 +46,8 @@ class QmmParamsC(C.Structure):
     _fields_ = [("bits", C.c_int32), ("group", C.c_int32), ("nibble_order", C.c_int32),
                 ("epilogue", C.c_int32), ("x", C.c_void_p), ("q", C.c_void_p), ("scale", C.c_void_p),
                 ("bias", C.c_void_p), ("residual", C.c_void_p), ("out", C.c_void_p),
-                ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("ldx", C.c_int64), ("ldo", C.c_int64)]
+                ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("ldx", C.c_int64), ("ldo", C.c_int64),
+                ("prologue", C.c_int32), ("eps", C.c_float), ("prologue_gain", C.c_void_p)]
 
 
 class DecoderConfigC(C.Structure):
@@ -96,6 +98,8 @@ PROTOTYPES = {
                                      C.c_float, C.c_float]),
     "b200_attention_scratch_bytes": (C.c_size_t, [_I64, _I, _I, _I64]),
     "b200_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64]),
+    "b200_attention_step": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64,
+                                 C.c_float, C.c_float]),
     "b200_silu_mul": (_I, [_VP, _VP, _VP, _VP, _I64, _I64]),
     "b200_tp_make_id": (_I, [_VP]),
     "b200_tp_create": (_I, [_VP, _VP, _I, _I, C.POINTER(_VP)]),

@@ -9,6 +9,7 @@
 // do the per-head norms, RoPE, the KV-cache shard and attention), o and down
 // by input columns, followed by an f32 all-reduce of the [B, hidden] partial
 // sums; the LM head by vocabulary rows, followed by an all-gather of logits.
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -72,7 +73,7 @@ struct b200_decoder {
   // activations (device, sized for max_batch)
   __nv_bfloat16 *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr,
                 *act = nullptr;
-  float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr;
+  float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr, *inv_freq = nullptr;
   bool use_graph = true;
   cudaStream_t capture_stream = nullptr;  // graphs are captured here (the caller's stream may be the legacy one)
   std::map<std::tuple<int, const void*, const void*, const void*>, cudaGraphExec_t> graphs;
@@ -82,8 +83,12 @@ struct b200_decoder {
 namespace {
 
 b200_status Qmm(b200_decoder* d, cudaStream_t stream, const b200_qweight& w, const void* x, void* out, int batch,
-                int64_t N, int64_t K, int epilogue, const void* residual) {
+                int64_t N, int64_t K, int epilogue, const void* residual, int prologue = B200_QMM_PRO_NONE,
+                const void* gain = nullptr) {
   b200_qmm_params p = {};
+  p.prologue = prologue;
+  p.prologue_gain = gain;
+  p.eps = d->cfg.rms_eps;
   p.bits = 4;
   p.group = 64;
   p.nibble_order = 0;
@@ -130,41 +135,61 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   const int64_t QKV = static_cast<int64_t>(c.heads + 2 * c.kv_heads) * c.head_dim;
   const bool tp = d->tp != nullptr && d->tp->world > 1;
 
+  // Up to 8 rows the RMSNorm in front of a projection is fused into its input
+  // staging (h is never written); beyond that it is its own kernel.
+  const bool fuse_norm = batch <= 8 && !tp;
   B200_TRY(b200_embed(ctx, stream, d->embed, tokens, d->x, batch, E));
-  B200_TRY(b200_rownorm(ctx, stream, 0, d->x, d->layers[0].attn_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
+  if (!fuse_norm)
+    B200_TRY(b200_rownorm(ctx, stream, 0, d->x, d->layers[0].attn_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
   for (int li = 0; li < c.layers; ++li) {
     const b200_decoder_layer& L = d->layers[li];
-    B200_TRY(Qmm(d, stream, L.qkv, d->h, d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr));
-    B200_TRY(b200_qk_norm_rope_cache(ctx, stream, d->qkv, L.q_norm, L.k_norm, d->q, L.k_cache, L.v_cache, pos, batch,
-                                     c.heads, c.kv_heads, c.head_dim, c.max_len, c.rope_theta, c.rms_eps));
-    B200_TRY(b200_attention_decode(ctx, stream, d->q, L.k_cache, L.v_cache, d->attn, pos, d->attn_scratch, batch,
-                                   c.heads, c.kv_heads, c.head_dim, c.max_len));
+    if (fuse_norm)
+      B200_TRY(Qmm(d, stream, L.qkv, d->x, d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM,
+                   L.attn_norm));
+    else
+      B200_TRY(Qmm(d, stream, L.qkv, d->h, d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr));
+    B200_TRY(b200_attention_step(ctx, stream, d->qkv, L.q_norm, L.k_norm, d->inv_freq, L.k_cache, L.v_cache, d->attn,
+                                 pos, d->attn_scratch, batch, c.heads, c.kv_heads, c.head_dim, c.max_len,
+                                 c.rope_theta, c.rms_eps));
     if (tp) {
       B200_TRY(Qmm(d, stream, L.o, d->attn, d->y32, batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr));
       B200_TRY(TpAllReduce(d->tp, stream, d->y32, static_cast<int64_t>(batch) * E, B200_F32));
       B200_TRY(ResidualNorm(d, stream, L.mlp_norm, batch));
     } else {
       B200_TRY(Qmm(d, stream, L.o, d->attn, d->x, batch, E, HD, B200_QMM_ADD_RESIDUAL, d->x));
-      B200_TRY(b200_rownorm(ctx, stream, 0, d->x, L.mlp_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
+      if (!fuse_norm)
+        B200_TRY(b200_rownorm(ctx, stream, 0, d->x, L.mlp_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
     }
-    B200_TRY(Qmm(d, stream, L.gate_up, d->h, d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
-                 nullptr));
-    B200_TRY(b200_silu_mul(ctx, stream, d->gu, d->act, batch, c.inter));
+    if (fuse_norm)
+      B200_TRY(Qmm(d, stream, L.gate_up, d->x, d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
+                   nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm));
+    else
+      B200_TRY(Qmm(d, stream, L.gate_up, d->h, d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
+                   nullptr));
     const void* next_norm = li + 1 < c.layers ? d->layers[li + 1].attn_norm : d->final_norm;
+    // silu(gate) * up is fused into the staging of the down projection's input
     if (tp) {
-      B200_TRY(Qmm(d, stream, L.down, d->act, d->y32, batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr));
+      B200_TRY(Qmm(d, stream, L.down, d->gu, d->y32, batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr,
+                   B200_QMM_PRO_SILU_MUL));
       B200_TRY(TpAllReduce(d->tp, stream, d->y32, static_cast<int64_t>(batch) * E, B200_F32));
       B200_TRY(ResidualNorm(d, stream, next_norm, batch));
     } else {
-      B200_TRY(Qmm(d, stream, L.down, d->act, d->x, batch, E, c.inter, B200_QMM_ADD_RESIDUAL, d->x));
-      B200_TRY(b200_rownorm(ctx, stream, 0, d->x, next_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
+      B200_TRY(Qmm(d, stream, L.down, d->gu, d->x, batch, E, c.inter, B200_QMM_ADD_RESIDUAL, d->x,
+                   B200_QMM_PRO_SILU_MUL));
+      if (!fuse_norm)
+        B200_TRY(b200_rownorm(ctx, stream, 0, d->x, next_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
     }
   }
   // LM head: bf16 rows, logits are the bf16-rounded products widened to f32 (qwen3.py:389-390)
   b200_qmm_params p = {};
   p.bits = 16;
   p.epilogue = B200_QMM_OUT_F32;
-  p.x = d->h;
+  p.x = fuse_norm ? d->x : d->h;
+  if (fuse_norm) {
+    p.prologue = B200_QMM_PRO_RMSNORM;
+    p.prologue_gain = d->final_norm;
+    p.eps = c.rms_eps;
+  }
   p.q = d->lm_head;
   p.out = tp ? d->logits_local : logits;
   p.M = batch;
@@ -224,6 +249,13 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
                    b200_attention_scratch_bytes(c.max_batch, c.heads, c.head_dim, c.max_len));
   if (e == cudaSuccess && tp != nullptr && tp->world > 1) e = Alloc(&d->logits_local, B * c.vocab);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = Alloc(&d->inv_freq, static_cast<size_t>(c.head_dim / 2));
+  if (e == cudaSuccess) {
+    std::vector<float> f(c.head_dim / 2);
+    for (int i = 0; i < c.head_dim / 2; ++i)
+      f[i] = static_cast<float>(1.0 / pow(static_cast<double>(c.rope_theta), static_cast<double>(2 * i) / c.head_dim));
+    e = cudaMemcpy(d->inv_freq, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice);
+  }
   if (e != cudaSuccess) {
     s = Fail(B200_RESOURCE_EXHAUSTED, "b200_decoder_create: %s", cudaGetErrorString(e));
     b200_decoder_destroy(d);
@@ -241,7 +273,7 @@ void b200_decoder_destroy(b200_decoder* d) {
   for (void* p : {static_cast<void*>(d->x), static_cast<void*>(d->h), static_cast<void*>(d->qkv),
                   static_cast<void*>(d->q), static_cast<void*>(d->attn), static_cast<void*>(d->gu),
                   static_cast<void*>(d->act), static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
-                  static_cast<void*>(d->logits_local)})
+                  static_cast<void*>(d->logits_local), static_cast<void*>(d->inv_freq)})
     if (p != nullptr) cudaFree(p);
   delete d;
 }

@@ -84,6 +84,11 @@ struct QmmArgs {
   int out_f32;
   const void* gemm_bias;
   void* aux;
+  // fused input transforms (b200_qmm_prologue)
+  int prologue;
+  int x_vec;                   // x rows allow 16-byte loads
+  float eps;
+  const __nv_bfloat16* gain;   // RMSNorm gain [K]
 };
 
 constexpr int kEpilogueGemm = 100;
@@ -161,7 +166,11 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   off += (static_cast<size_t>(groups_cta) * MP * 4 + 127) & ~static_cast<size_t>(127);
   uint4* xs = reinterpret_cast<uint4*>(smem + off);                  // [groups_cta][2][M][4] x 16 B
   off += (static_cast<size_t>(groups_cta) * a.M * 128 + 127) & ~static_cast<size_t>(127);
+  float2* so = reinterpret_cast<float2*>(smem + off);                // [groups_cta][R] (scale, offset)
+  if (GROUPED) off += (static_cast<size_t>(groups_cta) * R * 8 + 127) & ~static_cast<size_t>(127);
   uint8_t* stage_base = smem + off;
+  __shared__ float ss_part[kConsumerWarps][8];
+  __shared__ float rinv[8];
   constexpr int kStageBytes = R * F::kRowStride;
 
   if (tid == 0) {
@@ -200,27 +209,117 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
     if (lane == 0) pdl_launch_dependents();
   } else {
     // ---------------- consumer warps
+    // Scales and offsets belong to the weights: fetch them before waiting on the
+    // previous kernel, as (s, b - 128 s) pairs laid out [group][row].
+    if (GROUPED) {
+      const int g0 = k_begin / kGroupK;
+      for (int i = tid; i < R * groups_cta; i += kConsumerThreads) {
+        const int r = i / groups_cta, gi = i - r * groups_cta;
+        // rows past N are clamped for the load; their results are never stored
+        const size_t idx = static_cast<size_t>(min(n0 + r, a.N - 1)) * a.scale_ld + g0 + gi;
+        const float sc = ldg_bf16(a.scale + idx);
+        // int4 registers hold 128 + q: fold the 128 into the offset
+        const float of = F::kBits == 4 ? fmaf(-128.0f, sc, ldg_bf16(a.bias + idx)) : 0.0f;
+        so[gi * R + r] = make_float2(sc, of);
+      }
+    }
     pdl_wait();  // x (and the residual) come from the previous kernel
-    // Stage x in register order: unit (m, group, t) = 16 inputs = two 16-byte pieces.
+    if (a.prologue == B200_QMM_PRO_RMSNORM) {
+      // 1 / rms of every full row of x (M <= 8), recomputed by each CTA
+      float ss[8];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        ss[m] = 0.0f;
+        if (m < a.M) {
+          const __nv_bfloat16* xr = a.x + static_cast<size_t>(m) * a.ldx;
+          if (a.x_vec) {
+            for (int i = tid * 8; i < a.K; i += kConsumerThreads * 8) {
+              const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr + i));
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                ss[m] = fmaf(bf16_lo(w[j]), bf16_lo(w[j]), ss[m]);
+                ss[m] = fmaf(bf16_hi(w[j]), bf16_hi(w[j]), ss[m]);
+              }
+            }
+          } else {
+            for (int i = tid; i < a.K; i += kConsumerThreads) {
+              const float v = __bfloat162float(xr[i]);
+              ss[m] = fmaf(v, v, ss[m]);
+            }
+          }
+        }
+        ss[m] = warp_sum(ss[m]);
+        if (lane == 0) ss_part[warp][m] = ss[m];
+      }
+      consumer_barrier();
+      if (tid < 8) {
+        float tsum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) tsum += ss_part[w][tid];
+        rinv[tid] = 1.0f / sqrtf(tsum / static_cast<float>(a.K) + a.eps);
+      }
+      consumer_barrier();
+    }
+    // Stage x in register order: unit (m, group, t) = 16 inputs = two runs of 8 (or one of 16).
     {
       const int units = a.M * groups_cta * 4;
       const int units_pad = (units + 31) & ~31;
+      constexpr bool kOneRun = FMT == kInt4Seq || FMT == kInt8;
       for (int u = tid; u < units_pad; u += kConsumerThreads) {
         const bool valid = u < units;
         const int ut = u & 3;
         const int ug = (u >> 2) % groups_cta;
         const int um = (u >> 2) / groups_cta;
         float sum = 0.0f;
-        uint32_t regs[8];
         if (valid) {
-          const unsigned short* xp = reinterpret_cast<const unsigned short*>(a.x) +
-                                     static_cast<size_t>(um) * a.ldx + k_begin + ug * kGroupK;
+          const int kbase = k_begin + ug * kGroupK;
+          const int run0 = kOneRun ? 16 * ut : 8 * ut;
+          const int run1 = kOneRun ? 16 * ut + 8 : 32 + 8 * ut;
+          float e[16];
+          auto load_run = [&](const __nv_bfloat16* base, int k, float* dst) {
+            if (a.x_vec) {
+              const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + k));
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                dst[2 * j] = bf16_lo(w[j]);
+                dst[2 * j + 1] = bf16_hi(w[j]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) dst[j] = ldg_bf16(base + k + j);
+            }
+          };
+          const __nv_bfloat16* xr = a.x + static_cast<size_t>(um) * a.ldx;
+          load_run(xr, kbase + run0, e);
+          load_run(xr, kbase + run1, e + 8);
+          if (a.prologue == B200_QMM_PRO_RMSNORM) {
+            float gn[16];
+            load_run(a.gain, kbase + run0, gn);
+            load_run(a.gain, kbase + run1, gn + 8);
+            const float rr = rinv[um];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) e[j] = bf16_round((e[j] * rr) * gn[j]);
+          } else if (a.prologue == B200_QMM_PRO_SILU_MUL) {
+            // x is [M, 2K]: gate in the first K columns, up in the last K
+            float up[16];
+            load_run(xr + a.K, kbase + run0, up);
+            load_run(xr + a.K, kbase + run1, up + 8);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float sig = bf16_round(1.0f / (1.0f + expf(-e[j])));
+              e[j] = bf16_round(bf16_round(e[j] * sig) * up[j]);
+            }
+          }
+          uint32_t regs[8];
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
-            const uint32_t lo = __ldg(xp + kmap<FMT>(ut, r, 0));
-            const uint32_t hi = __ldg(xp + kmap<FMT>(ut, r, 1));
-            regs[r] = lo | (hi << 16);
-            sum += bf16_bits_to_f32(lo) + bf16_bits_to_f32(hi);
+            const int k0 = kmap<FMT>(0, r, 0), k1 = kmap<FMT>(0, r, 1);
+            const int l0 = kOneRun ? k0 : (k0 & 7) + 8 * (k0 >> 5);
+            const int l1 = kOneRun ? k1 : (k1 & 7) + 8 * (k1 >> 5);
+            regs[r] = pack_bf16(e[l0], e[l1]);
+            sum += e[l0] + e[l1];
           }
           xs[((ug * 2 + 0) * a.M + um) * 4 + ut] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
           xs[((ug * 2 + 1) * a.M + um) * 4 + ut] = make_uint4(regs[4], regs[5], regs[6], regs[7]);
@@ -250,7 +349,6 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       const int chunk_groups = min(kChunkK, a.k_per_cta - c * kChunkK) / kGroupK;
       if (warp < chunk_groups) {
         const int gl = c * (kChunkK / kGroupK) + warp;   // group within this CTA's slice
-        const int gg = k_begin / kGroupK + gl;           // group within the row
         uint32_t xf[MB][8];
         float xs2[MB][2];
 #pragma unroll
@@ -277,16 +375,9 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
           const int r0 = rt * 16 + g, r1 = r0 + 8;
           float s0 = 1.0f, s1 = 1.0f, o0 = 0.0f, o1 = 0.0f;
           if (GROUPED) {
-            // rows past N are clamped for the load; their results are never stored
-            const size_t i0 = static_cast<size_t>(min(n0 + r0, a.N - 1)) * a.scale_ld + gg;
-            const size_t i1 = static_cast<size_t>(min(n0 + r1, a.N - 1)) * a.scale_ld + gg;
-            s0 = ldg_bf16(a.scale + i0);
-            s1 = ldg_bf16(a.scale + i1);
-            if (F::kBits == 4) {
-              // the registers hold 128 + q: fold the 128 into the offset
-              o0 = fmaf(-128.0f, s0, ldg_bf16(a.bias + i0));
-              o1 = fmaf(-128.0f, s1, ldg_bf16(a.bias + i1));
-            }
+            const float2 p0 = so[gl * R + r0], p1 = so[gl * R + r1];
+            s0 = p0.x; o0 = p0.y;
+            s1 = p1.x; o1 = p1.y;
           }
           uint32_t a0[8], a1[8];
           load_a<FMT>(stage + r0 * F::kRowStride, t, a0);
@@ -415,6 +506,7 @@ size_t SmemFor(const Plan& pl, int M, int k_per_cta) {
   off += static_cast<size_t>(R) * MP * 4;
   off += (static_cast<size_t>(groups) * MP * 4 + 127) & ~static_cast<size_t>(127);
   off += (static_cast<size_t>(groups) * M * 128 + 127) & ~static_cast<size_t>(127);
+  if (pl.grouped) off += (static_cast<size_t>(groups) * R * 8 + 127) & ~static_cast<size_t>(127);
   off += static_cast<size_t>(pl.stages) * R * ChunkRowStride(pl.fmt);
   return off;
 }
@@ -437,15 +529,21 @@ b200_status Validate(const b200_qmm_params* p) {
   if (p->bits == 4 && p->nibble_order != 0 && p->nibble_order != 1)
     return Fail(B200_INVALID_ARGUMENT, "b200_qmm: nibble_order must be 0 or 1");
   if (p->epilogue < 0 || p->epilogue > 3) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: unknown epilogue %d", p->epilogue);
+  if (p->prologue < 0 || p->prologue > 2) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: unknown prologue %d", p->prologue);
+  if (p->prologue == B200_QMM_PRO_RMSNORM && p->M > 8)
+    return Fail(B200_UNIMPLEMENTED, "b200_qmm: the fused RMSNorm takes up to 8 rows (run b200_rownorm first)");
   if (p->M == 0 || p->N == 0) return B200_OK;
+  if (p->prologue == B200_QMM_PRO_RMSNORM && p->prologue_gain == nullptr)
+    return Fail(B200_INVALID_ARGUMENT, "b200_qmm: fused RMSNorm without a gain");
   if (p->x == nullptr || p->q == nullptr || p->out == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: null buffer");
   if (p->bits != 16 && p->scale == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: null scale");
   if (p->bits == 4 && p->bias == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: int4 needs a bias (offset) buffer");
   if (p->epilogue == B200_QMM_ADD_RESIDUAL && p->residual == nullptr)
     return Fail(B200_INVALID_ARGUMENT, "b200_qmm: residual epilogue without a residual buffer");
   if (!Aligned(p->q, 16)) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: q must be 16-byte aligned (bulk copies)");
-  const int64_t ldx = p->ldx ? p->ldx : p->K, ldo = p->ldo ? p->ldo : p->N;
-  if (ldx < p->K || ldo < p->N) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: leading dimension smaller than row length");
+  const int64_t xcols = p->prologue == B200_QMM_PRO_SILU_MUL ? 2 * p->K : p->K;
+  const int64_t ldx = p->ldx ? p->ldx : xcols, ldo = p->ldo ? p->ldo : p->N;
+  if (ldx < xcols || ldo < p->N) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: leading dimension smaller than row length");
   if (p->K == 0) return Fail(B200_UNIMPLEMENTED, "b200_qmm: K = 0");
   return B200_OK;
 }
@@ -564,6 +662,7 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
   a.K = static_cast<int>(K);
   a.ldx = static_cast<int>(ld_vec);
   a.ldo = static_cast<int>(R);
+  a.x_vec = Aligned(vecs, 16) && ld_vec % 8 == 0;
   a.k_per_cta = a.K / pl.split;
   a.epilogue = kEpilogueGemm;
   a.stages = pl.stages;
@@ -619,8 +718,12 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   a.M = static_cast<int>(p->M);
   a.N = static_cast<int>(p->N);
   a.K = static_cast<int>(p->K);
-  a.ldx = static_cast<int>(p->ldx ? p->ldx : p->K);
+  a.ldx = static_cast<int>(p->ldx ? p->ldx : (p->prologue == B200_QMM_PRO_SILU_MUL ? 2 * p->K : p->K));
   a.ldo = static_cast<int>(p->ldo ? p->ldo : p->N);
+  a.prologue = p->prologue;
+  a.eps = p->eps;
+  a.gain = static_cast<const __nv_bfloat16*>(p->prologue_gain);
+  a.x_vec = Aligned(p->x, 16) && a.ldx % 8 == 0 && (p->prologue != B200_QMM_PRO_RMSNORM || Aligned(p->prologue_gain, 16));
   a.scale_ld = p->bits == 16 ? 0 : static_cast<int>(p->K / p->group);
   a.k_per_cta = a.K / pl.split;
   a.epilogue = p->epilogue;

@@ -80,16 +80,17 @@ def dequantize(w, dtype=None, ctx=None):
     return out
 
 
-def linear(x, w, residual=None, out_f32=False, ctx=None, stream=None):
+def linear(x, w, residual=None, out_f32=False, rms_gain=None, eps=1e-6, silu_mul=False, ctx=None, stream=None):
     """≙ linear (qwen3.py:218-230): x @ w.T for an [out, in] weight, bf16 or
     quantised, up to ROWS_MAX rows; result in x's dtype (bf16).  `residual`
     fuses the x + linear(...) of the decoder layer; out_f32 gives the LM head's
-    f32 logits."""
+    f32 logits.  rms_gain fuses linear(rms_norm(x, rms_gain, eps), w) (up to 8
+    rows); silu_mul fuses linear(silu(gate) * up, w) for x = [gate | up]."""
     torch = _torch()
     ctx = ctx or default_context()
     bits, group, order, q, s, b, N, K = _describe(w)
     lead = x.shape[:-1]
-    x2 = x.reshape(-1, K)
+    x2 = x.reshape(-1, 2 * K if silu_mul else K)
     M = x2.shape[0]
     out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     p = _lib.QmmParamsC()
@@ -101,7 +102,11 @@ def linear(x, w, residual=None, out_f32=False, ctx=None, stream=None):
     p.residual = residual.data_ptr() if residual is not None else None
     p.out = out.data_ptr()
     p.M, p.N, p.K = M, N, K
-    p.ldx, p.ldo = x2.stride(0) if M > 0 else K, N
+    p.ldx, p.ldo = x2.stride(0) if M > 0 else 0, N
+    if rms_gain is not None:
+        p.prologue, p.eps, p.prologue_gain = _lib.QMM_PRO_RMSNORM, eps, rms_gain.data_ptr()
+    elif silu_mul:
+        p.prologue = _lib.QMM_PRO_SILU_MUL
     _lib.check(_lib.lib().b200_qmm_run(ctx.handle, stream or _lib.current_stream(), C.byref(p)))
     return out.reshape(*lead, N)
 

@@ -78,6 +78,68 @@ def test_pieces_against_oracle(B, H, KV, D, S, pos):
     assert rel_rms_err(host(out).astype(np.float32), a_ref.reshape(B, H, D).astype(np.float32)) <= 2e-2
 
 
+@pytest.mark.parametrize("B,H,KV,D,S,pos", [(2, 4, 2, 64, 48, 30), (3, 8, 2, 128, 300, 299), (1, 32, 8, 128, 2176, 2048),
+                                            (2, 4, 4, 128, 130, 0), (2, 8, 1, 128, 256, 64), (1, 2, 2, 64, 72, 63)])
+def test_fused_attention_step(B, H, KV, D, S, pos):
+    """q/k RMSNorm + RoPE, the cache writes and attention in one call, against the oracle."""
+    import torch
+    from oracle.rownorm import rms_norm
+    p = pkg()
+    L = p.lib()
+    rng = np.random.default_rng(21)
+    qkv = rng.standard_normal((B, (H + 2 * KV) * D), dtype=np.float32).astype(bf16)
+    qn = (1 + 0.1 * rng.standard_normal(D, dtype=np.float32)).astype(bf16)
+    kn = (1 + 0.1 * rng.standard_normal(D, dtype=np.float32)).astype(bf16)
+    kc = rng.standard_normal((B, KV, S, D), dtype=np.float32).astype(bf16)
+    vc = rng.standard_normal((B, KV, D, S), dtype=np.float32).astype(bf16)
+    kc[:, :, pos:] = np.float32("nan")      # slots at and past pos hold junk that must never be read
+    vc[:, :, :, pos:] = np.float32("nan")
+    qkvd, qnd, knd, kd, vd = dev(qkv), dev(qn), dev(kn), dev(kc), dev(vc)
+    out = torch.empty((B, H, D), dtype=torch.bfloat16, device="cuda")
+    posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    scratch = torch.empty(L.b200_attention_scratch_bytes(B, H, D, S) // 4, device="cuda")
+    _call(p, L.b200_attention_step, qkvd.data_ptr(), qnd.data_ptr(), knd.data_ptr(), None, kd.data_ptr(), vd.data_ptr(),
+          out.data_ptr(), posd.data_ptr(), scratch.data_ptr(), B, H, KV, D, S, 1e6, 1e-6)
+    positions = np.full((B,), pos)
+    q_ref = odec.rope(rms_norm(qkv[:, :H * D].reshape(B, H, D), qn, 1e-6), positions, 1e6)
+    k_ref = odec.rope(rms_norm(qkv[:, H * D:(H + KV) * D].reshape(B, KV, D), kn, 1e-6), positions, 1e6)
+    v_ref = qkv[:, (H + KV) * D:].reshape(B, KV, D)
+    gk, gv = host(kd), host(vd)
+    assert rel_rms_err(gk[:, :, pos].astype(np.float32), k_ref.astype(np.float32)) <= 2e-2
+    assert np.array_equal(gv[:, :, :, pos].view(np.uint16), v_ref.view(np.uint16))
+    mask = np.ones(S, bool)
+    mask[pos] = False
+    assert np.array_equal(gk[:, :, mask].view(np.uint16), kc[:, :, mask].view(np.uint16))
+    assert np.array_equal(gv[:, :, :, mask].view(np.uint16), vc[:, :, :, mask].view(np.uint16))
+    kc2, vc2 = kc.copy(), vc.copy()
+    kc2[:, :, pos] = k_ref
+    vc2[:, :, :, pos] = v_ref
+    a_ref = odec.attention_decode(q_ref.reshape(B, KV, H // KV, D), kc2, vc2, pos + 1, D ** -0.5)
+    assert rel_rms_err(host(out).astype(np.float32), a_ref.reshape(B, H, D).astype(np.float32)) <= 2e-2
+    assert p.default_context().error() == 0
+
+
+def test_attention_step_refuses_a_position_outside_the_cache():
+    import torch
+    p = pkg()
+    L = p.lib()
+    ctx = p.Context(0)
+    B, H, KV, D, S = 1, 2, 1, 64, 32
+    qkv = torch.zeros((B, (H + 2 * KV) * D), dtype=torch.bfloat16, device="cuda")
+    g = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    kc = torch.zeros((B, KV, S, D), dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros((B, KV, D, S), dtype=torch.bfloat16, device="cuda")
+    out = torch.full((B, H, D), 5.0, dtype=torch.bfloat16, device="cuda")
+    posd = torch.tensor([S], dtype=torch.int32, device="cuda")   # one past the end
+    scratch = torch.empty(L.b200_attention_scratch_bytes(B, H, D, S) // 4, device="cuda")
+    p._lib.check(L.b200_attention_step(ctx.handle, p._lib.current_stream(), qkv.data_ptr(), g.data_ptr(), g.data_ptr(),
+                                       None, kc.data_ptr(), vc.data_ptr(), out.data_ptr(), posd.data_ptr(),
+                                       scratch.data_ptr(), B, H, KV, D, S, 1e6, 1e-6))
+    torch.cuda.synchronize()
+    assert ctx.error() == p._lib.INVALID_ARGUMENT          # reported through the device status word
+    assert torch.all(out == 5.0) and torch.all(kc == 0) and torch.all(vc == 0)
+
+
 def test_silu_mul_and_embed():
     import torch
     p = pkg()

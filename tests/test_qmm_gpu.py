@@ -179,3 +179,44 @@ def test_edge_cases():
         p.qwen3.linear(torch.zeros((33, 64), dtype=torch.bfloat16, device="cuda"), w)
     assert e.value.status == p._lib.UNIMPLEMENTED
     assert p.default_context().error() == 0
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("bits", [4, 16])
+def test_fused_rmsnorm_prologue(m, bits):
+    """linear(rms_norm(x, gain, eps), w) with the norm fused into the input staging."""
+    from oracle import rownorm
+    p = pkg()
+    k, n = 1024, 512
+    x, packed, s, b, _ = inputs.config4(m, k, n)
+    gain = (1 + 0.1 * np.random.default_rng(3).standard_normal(k, dtype=np.float32)).astype(bf16)
+    h = rownorm.rms_norm(x, gain, 1e-6)
+    if bits == 4:
+        w = _w4(packed, s, b)
+        want = quant.qmm(h, quant.bl_unpack_int4(packed), s, b, np.float32)
+    else:
+        wm = (np.random.default_rng(4).standard_normal((n, k), dtype=np.float32) * 0.02).astype(bf16)
+        w = dev(wm)
+        want = h.astype(np.float64) @ wm.astype(np.float64).T
+    got = host(p.qwen3.linear(dev(x), w, rms_gain=dev(gain), eps=1e-6)).astype(np.float32)
+    assert rel_rms_err(got, want) <= TOL
+    # and it equals the two-kernel path to within bf16 rounding of h
+    two = host(p.qwen3.linear(p.rows.rms_norm(dev(x), dev(gain), 1e-6), w)).astype(np.float32)
+    assert rel_rms_err(got, two) <= TOL
+    with pytest.raises(p.B200Error):
+        import torch
+        p.qwen3.linear(torch.zeros((9, k), dtype=torch.bfloat16, device="cuda"), w, rms_gain=dev(gain))
+
+
+@pytest.mark.parametrize("m", [1, 8, 32])
+def test_fused_silu_mul_prologue(m):
+    """linear(silu(gate) * up, w) for x = [gate | up]."""
+    from oracle import decoder as odec
+    p = pkg()
+    k, n = 1536, 256
+    _, packed, s, b, _ = inputs.config4(1, k, n)
+    gu = (np.random.default_rng(8).standard_normal((m, 2 * k), dtype=np.float32) * 1.5).astype(bf16)
+    act = odec.silu_mul(gu[:, :k], gu[:, k:])
+    want = quant.qmm(act, quant.bl_unpack_int4(packed), s, b, np.float32)
+    got = host(p.qwen3.linear(dev(gu), _w4(packed, s, b), silu_mul=True)).astype(np.float32)
+    assert got.shape == (m, n) and rel_rms_err(got, want) <= TOL
