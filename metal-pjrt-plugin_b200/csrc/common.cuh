@@ -52,6 +52,9 @@ inline int64_t CeilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline bool Aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline int DtypeSize(int dt) { return dt == B200_F32 ? 4 : 2; }
 
+// B200_NO_PDL=1 launches every kernel with plain stream ordering (an A/B switch).
+bool PdlDisabled();
+
 // Launch helper: optional programmatic dependent launch (the kernel must call
 // pdl_wait() before touching anything an earlier kernel wrote) and optional
 // thread-block cluster along y.
@@ -72,7 +75,7 @@ cudaError_t Launch(const LaunchCfg& lc, void (*kernel)(KArgs...), Args&&... args
   cfg.stream = lc.stream;
   cudaLaunchAttribute attrs[2];
   unsigned n = 0;
-  if (lc.pdl) {
+  if (lc.pdl && !PdlDisabled()) {
     attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
@@ -159,17 +162,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Waits for the phase with the given parity, at most ~2 s.  Returns false when
-// it gave up; the caller reports B200_TIMEOUT through the status word and
-// leaves the pipeline.
+// Waits for the phase with the given parity, bounded by ~4e9 SM cycles (about
+// two seconds).  Returns false when it gave up; the caller reports B200_TIMEOUT
+// through the status word and leaves the pipeline.  The SM cycle counter is
+// read only after a few thousand failed polls (each poll may itself suspend the
+// thread for a while), so the common case costs nothing but the polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i)
+    for (int i = 0; i < 1024; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > 2000000000ull) return false;
+    if (clock64() - t0 > 4000000000ll) return false;
   }
 }
 // 1-D bulk copy global -> this CTA's shared memory, completion on `bar`.
@@ -194,6 +201,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// d = a . b (no accumulator input: the zero registers cost no instruction)
+__device__ __forceinline__ void mma_bf16_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 // Epilogue activation in f32 (formulas of metal_pjrt/kernels/steel_gemm.metal:58-66).

@@ -2,6 +2,8 @@
 // Replaces the reference's rt::Device error model (sticky first error,
 // metal_pjrt/runtime/metal_runtime.h:43-53) and its host-side fault
 // injection (metal_pjrt/runtime/metal_runtime.cc:1646-1653).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -31,6 +33,14 @@ b200_status Stick(b200_context* ctx, b200_status code) {
     ctx->sticky_message = g_error;
   }
   return code;
+}
+
+bool PdlDisabled() {
+  static const bool off = [] {
+    const char* v = std::getenv("B200_NO_PDL");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return off;
 }
 
 b200_status BeginLaunch(b200_context* ctx) {

@@ -31,10 +31,10 @@ using namespace b200;
 
 namespace {
 
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;  // + one producer warp
-constexpr int kChunkK = 512;                     // inputs per pipeline stage: 8 groups
+constexpr int kCopyBytes = 2048;                 // bytes of one weight row per bulk copy (RT = 1)
 constexpr int kGroupK = 64;
 
 enum Format { kInt4Seq = 0, kInt4Half = 1, kInt8 = 2, kBf16 = 3 };
@@ -42,9 +42,7 @@ enum Format { kInt4Seq = 0, kInt4Half = 1, kInt8 = 2, kBf16 = 3 };
 template <int FMT>
 struct Fmt {
   static constexpr int kBits = FMT == kInt8 ? 8 : (FMT == kBf16 ? 16 : 4);
-  static constexpr int kChunkRowBytes = kChunkK * kBits / 8;  // 256 / 512 / 1024
   static constexpr int kPad = kBits == 4 ? 32 : 64;           // keeps the quad reads conflict-free
-  static constexpr int kRowStride = kChunkRowBytes + kPad;
   static constexpr int kGroupBytes = kGroupK * kBits / 8;     // 32 / 64 / 128
 };
 
@@ -87,6 +85,8 @@ struct QmmArgs {
   // fused input transforms (b200_qmm_prologue)
   int prologue;
   int x_vec;                   // x rows allow 16-byte loads
+  int scale_vec;               // scale / offset rows allow 16-byte loads of eight groups
+  int tiles;                   // row tiles in all (ceil(N / (16 RT)))
   float eps;
   const __nv_bfloat16* gain;   // RMSNorm gain [K]
 };
@@ -135,43 +135,90 @@ __device__ __forceinline__ void consumer_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
 
-// FMT: storage format; MB: batch blocks of 8; RT: 16-row tiles per CTA;
+// One output element: the per-channel scale (if any), then the epilogue.
+template <int FMT, bool GROUPED>
+__device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, int n) {
+  if (!GROUPED && Fmt<FMT>::kBits != 16) v *= ldg_bf16(a.scale + n);
+  if (a.epilogue == kEpilogueGemm) {
+    const size_t o = static_cast<size_t>(m) * a.out_vec_stride + static_cast<size_t>(n) * a.out_row_stride;
+    v *= a.alpha;
+    const int bi = a.bias_by_vec ? m : n;
+    if (a.out_f32) {
+      if (a.gemm_bias != nullptr) v += static_cast<const float*>(a.gemm_bias)[bi];
+      if (a.aux != nullptr) static_cast<float*>(a.aux)[o] = v;
+      static_cast<float*>(a.out)[o] = apply_act(a.act, v);
+    } else {
+      if (a.gemm_bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(a.gemm_bias)[bi]);
+      if (a.aux != nullptr) static_cast<__nv_bfloat16*>(a.aux)[o] = __float2bfloat16_rn(v);
+      static_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(apply_act(a.act, v));
+    }
+    return;
+  }
+  const float y = bf16_round(v);
+  const size_t o = static_cast<size_t>(m) * a.ldo + n;
+  if (a.epilogue == B200_QMM_OUT_F32_RAW) {
+    reinterpret_cast<float*>(a.out)[o] = v;
+  } else if (a.epilogue == B200_QMM_OUT_F32) {
+    reinterpret_cast<float*>(a.out)[o] = y;
+  } else if (a.epilogue == B200_QMM_ADD_RESIDUAL) {
+    reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(__bfloat162float(a.residual[o]) + y);
+  } else {
+    reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(v);
+  }
+}
+
+// FMT: storage format; MB: batch blocks of 8; RT: 16-row tiles per CTA tile;
 // GROUPED: a scale (and offset) per 64 inputs, else one scale per row applied at the end.
-template <int FMT, int MB, int RT, bool GROUPED>
+//
+// grid = (CTAs, split).  With split == 1 a CTA is persistent: it walks row tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... and stages x (and fused transforms)
+// once.  With split > 1 the grid has one CTA per (tile, K slice) and the slices
+// of a tile form a cluster that reduces through distributed shared memory.
+// KG > 0: the CTA's K slice is exactly KG groups (and MB == 1): every warp owns
+// a compile-time set of KG / 16 groups, keeps their x fragments in registers for
+// all row tiles, and its loop over them is fully unrolled.  KG == 0: any K.
+template <int FMT, int MB, int RT, bool GROUPED, int KG>
 __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   using F = Fmt<FMT>;
   constexpr int R = 16 * RT;
   constexpr int MP = 8 * MB;
+  // One pipeline stage holds R rows x kChunkK inputs; a row's share arrives as ONE
+  // bulk copy (small copies are bound by the copy engine's request rate, not by HBM).
+  constexpr int kChunkRowBytes = kCopyBytes / RT;
+  constexpr int kChunkK = kChunkRowBytes * 8 / F::kBits;
+  constexpr int kRowStride = kChunkRowBytes + F::kPad;
+  constexpr int kStageBytes = R * kRowStride;
   extern __shared__ __align__(128) uint8_t smem[];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * R;
-  const int rows_valid = min(R, a.N - n0);
   const int split = gridDim.y;
+  const bool persistent = split == 1;
   const int k_begin = blockIdx.y * a.k_per_cta;
   const int groups_cta = a.k_per_cta / kGroupK;
   const int n_chunks = (a.k_per_cta + kChunkK - 1) / kChunkK;
   const int NS = a.stages;
   const size_t row_bytes_total = static_cast<size_t>(a.K) * F::kBits / 8;
+  const int n_my = (a.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int n_units = n_my * n_chunks;
 
   // ---- shared memory carve-up -------------------------------------------------
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + NS;
   size_t off = (static_cast<size_t>(2 * NS) * 8 + 127) & ~static_cast<size_t>(127);
-  float* red = reinterpret_cast<float*>(smem + off);                 // [R][MP]
-  off += static_cast<size_t>(R) * MP * 4;
+  float* red = reinterpret_cast<float*>(smem + off);                 // [2][R][MP]
+  off += static_cast<size_t>(2) * R * MP * 4;
   float* xsum = reinterpret_cast<float*>(smem + off);                // [groups_cta][MP]
   off += (static_cast<size_t>(groups_cta) * MP * 4 + 127) & ~static_cast<size_t>(127);
   uint4* xs = reinterpret_cast<uint4*>(smem + off);                  // [groups_cta][2][M][4] x 16 B
   off += (static_cast<size_t>(groups_cta) * a.M * 128 + 127) & ~static_cast<size_t>(127);
-  float2* so = reinterpret_cast<float2*>(smem + off);                // [groups_cta][R] (scale, offset)
-  if (GROUPED) off += (static_cast<size_t>(groups_cta) * R * 8 + 127) & ~static_cast<size_t>(127);
+  float2* so = reinterpret_cast<float2*>(smem + off);                // [2][groups_cta][R] (scale, offset)
+  const int so_buf = groups_cta * R;
+  if (GROUPED) off += (static_cast<size_t>(2) * so_buf * 8 + 127) & ~static_cast<size_t>(127);
   uint8_t* stage_base = smem + off;
   __shared__ float ss_part[kConsumerWarps][8];
   __shared__ float rinv[8];
-  constexpr int kStageBytes = R * F::kRowStride;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -180,49 +227,88 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
     }
     mbar_fence_init();
   }
-  for (int i = tid; i < R * MP; i += kThreads) red[i] = 0.0f;
+  for (int i = tid; i < 2 * R * MP; i += kThreads) red[i] = 0.0f;
   for (int i = tid; i < groups_cta * MP; i += kThreads) xsum[i] = 0.0f;
   __syncthreads();
 
-  bool dead = false;  // a bounded wait gave up: leave the pipeline, keep the barriers below
+  bool dead = false;  // a bounded wait gave up: skip the work, keep every barrier
 
   if (warp == kConsumerWarps) {
     // ---------------- producer warp: weights only, independent of earlier kernels
-    const uint8_t* src0 = a.q + static_cast<size_t>(n0) * row_bytes_total +
-                          static_cast<size_t>(k_begin) * F::kBits / 8;
-    for (int c = 0; c < n_chunks && !dead; ++c) {
-      const int s = c % NS, use = c / NS;
-      if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
+    const int first_fill = min(n_units, NS);
+    for (int u = 0; u < n_units; ++u) {
+      const int ti = u / n_chunks, c = u - ti * n_chunks;
+      const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
+      const int rows_valid = min(R, a.N - n0);
+      const int s = u % NS, use = u / NS;
+      if (!dead && use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
         report_timeout(a.status, 100 + s);
         dead = true;
-        break;
       }
-      const int chunk_k = min(kChunkK, a.k_per_cta - c * kChunkK);
-      const uint32_t bytes_row = static_cast<uint32_t>(chunk_k * F::kBits / 8);
-      if (lane == 0) mbar_expect_tx(&full[s], bytes_row * rows_valid);
-      __syncwarp();
-      uint8_t* dst = stage_base + static_cast<size_t>(s) * kStageBytes;
-      const uint8_t* src = src0 + static_cast<size_t>(c) * F::kChunkRowBytes;
-      for (int r = lane; r < rows_valid; r += 32)
-        bulk_g2s(dst + r * F::kRowStride, src + static_cast<size_t>(r) * row_bytes_total, bytes_row, &full[s]);
+      if (!dead) {
+        const int chunk_k = min(kChunkK, a.k_per_cta - c * kChunkK);
+        const uint32_t bytes_row = static_cast<uint32_t>(chunk_k * F::kBits / 8);
+        if (lane == 0) mbar_expect_tx(&full[s], bytes_row * rows_valid);
+        __syncwarp();
+        uint8_t* dst = stage_base + static_cast<size_t>(s) * kStageBytes;
+        const uint8_t* src = a.q + static_cast<size_t>(n0) * row_bytes_total +
+                             (static_cast<size_t>(k_begin) + static_cast<size_t>(c) * kChunkK) * F::kBits / 8;
+        for (int r = lane; r < rows_valid; r += 32)
+          bulk_g2s(dst + r * kRowStride, src + static_cast<size_t>(r) * row_bytes_total, bytes_row, &full[s]);
+      }
+      if (u == first_fill - 1 && lane == 0) pdl_launch_dependents();
     }
-    if (lane == 0) pdl_launch_dependents();
   } else {
     // ---------------- consumer warps
-    // Scales and offsets belong to the weights: fetch them before waiting on the
-    // previous kernel, as (s, b - 128 s) pairs laid out [group][row].
-    if (GROUPED) {
-      const int g0 = k_begin / kGroupK;
-      for (int i = tid; i < R * groups_cta; i += kConsumerThreads) {
-        const int r = i / groups_cta, gi = i - r * groups_cta;
-        // rows past N are clamped for the load; their results are never stored
-        const size_t idx = static_cast<size_t>(min(n0 + r, a.N - 1)) * a.scale_ld + g0 + gi;
-        const float sc = ldg_bf16(a.scale + idx);
-        // int4 registers hold 128 + q: fold the 128 into the offset
-        const float of = F::kBits == 4 ? fmaf(-128.0f, sc, ldg_bf16(a.bias + idx)) : 0.0f;
-        so[gi * R + r] = make_float2(sc, of);
+    // Scales and offsets belong to the weights, so the first tile's are fetched
+    // before waiting on the previous kernel; a later tile's are fetched into
+    // registers while the tile before it is computed.  Stored packed (scale,
+    // offset) as [group][row].
+    const int g0 = k_begin / kGroupK;
+    const int nch = R * (groups_cta / 8);
+    uint4 sreg = make_uint4(0, 0, 0, 0), breg = make_uint4(0, 0, 0, 0);
+    auto scale_load = [&](int n0) {
+      if (GROUPED && a.scale_vec && tid < nch) {
+        const int c = tid / R, r = tid - c * R;
+        const size_t o = static_cast<size_t>(min(n0 + r, a.N - 1)) * a.scale_ld + g0 + 8 * c;
+        sreg = __ldg(reinterpret_cast<const uint4*>(a.scale + o));
+        if (F::kBits == 4) breg = __ldg(reinterpret_cast<const uint4*>(a.bias + o));
       }
-    }
+    };
+    // int4 registers hold 128 + q: the 128 is folded into the offset here
+    auto put8 = [&](float2* dstbuf, int c, int r, const uint4& sv, const uint4& bv) {
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+      const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sc = (j & 1) ? bf16_hi(sw[j >> 1]) : bf16_lo(sw[j >> 1]);
+        const float bi = (j & 1) ? bf16_hi(bw[j >> 1]) : bf16_lo(bw[j >> 1]);
+        dstbuf[(8 * c + j) * R + r] = make_float2(sc, F::kBits == 4 ? fmaf(-128.0f, sc, bi) : 0.0f);
+      }
+    };
+    auto scale_store = [&](int n0, float2* dstbuf) {
+      if (!GROUPED) return;
+      if (a.scale_vec) {
+        if (tid < nch) put8(dstbuf, tid / R, tid % R, sreg, breg);
+        for (int idx = tid + kConsumerThreads; idx < nch; idx += kConsumerThreads) {   // rarely taken
+          const int c = idx / R, r = idx - c * R;
+          const size_t o = static_cast<size_t>(min(n0 + r, a.N - 1)) * a.scale_ld + g0 + 8 * c;
+          const uint4 sv = __ldg(reinterpret_cast<const uint4*>(a.scale + o));
+          const uint4 bv = F::kBits == 4 ? __ldg(reinterpret_cast<const uint4*>(a.bias + o)) : make_uint4(0, 0, 0, 0);
+          put8(dstbuf, c, r, sv, bv);
+        }
+      } else {
+        for (int i = tid; i < R * groups_cta; i += kConsumerThreads) {
+          const int r = i / groups_cta, gi = i - r * groups_cta;
+          // rows past N are clamped for the load; their results are never stored
+          const size_t o = static_cast<size_t>(min(n0 + r, a.N - 1)) * a.scale_ld + g0 + gi;
+          const float sc = ldg_bf16(a.scale + o);
+          dstbuf[gi * R + r] = make_float2(sc, F::kBits == 4 ? fmaf(-128.0f, sc, ldg_bf16(a.bias + o)) : 0.0f);
+        }
+      }
+    };
+    scale_load(static_cast<int>(blockIdx.x) * R);
+    scale_store(static_cast<int>(blockIdx.x) * R, so);
     pdl_wait();  // x (and the residual) come from the previous kernel
     if (a.prologue == B200_QMM_PRO_RMSNORM) {
       // 1 / rms of every full row of x (M <= 8), recomputed by each CTA
@@ -339,147 +425,179 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[rt][mb][i] = 0.0f;
 
-    for (int c = 0; c < n_chunks; ++c) {
-      const int s = c % NS;
-      if (!mbar_wait_bounded(&full[s], (c / NS) & 1)) {
-        report_timeout(a.status, 200 + s);
-        dead = true;
-        break;
-      }
-      const int chunk_groups = min(kChunkK, a.k_per_cta - c * kChunkK) / kGroupK;
-      if (warp < chunk_groups) {
-        const int gl = c * (kChunkK / kGroupK) + warp;   // group within this CTA's slice
-        uint32_t xf[MB][8];
-        float xs2[MB][2];
+    // x fragments (and per-group sums of x) of one group for this lane
+    auto load_x = [&](int gl, uint32_t (&xf)[MB][8], float (&xs2)[MB][2]) {
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-          const int m = mb * 8 + g;
-          if (m < a.M) {
-            const uint4 v0 = xs[((gl * 2 + 0) * a.M + m) * 4 + t];
-            const uint4 v1 = xs[((gl * 2 + 1) * a.M + m) * 4 + t];
-            xf[mb][0] = v0.x; xf[mb][1] = v0.y; xf[mb][2] = v0.z; xf[mb][3] = v0.w;
-            xf[mb][4] = v1.x; xf[mb][5] = v1.y; xf[mb][6] = v1.z; xf[mb][7] = v1.w;
-          } else {
-#pragma unroll
-            for (int r = 0; r < 8; ++r) xf[mb][r] = 0u;
-          }
-          if (F::kBits == 4) {
-            const float2 v = *reinterpret_cast<const float2*>(&xsum[gl * MP + mb * 8 + 2 * t]);
-            xs2[mb][0] = v.x;
-            xs2[mb][1] = v.y;
-          }
-        }
-        const uint8_t* stage = stage_base + static_cast<size_t>(s) * kStageBytes + warp * F::kGroupBytes;
-#pragma unroll
-        for (int rt = 0; rt < RT; ++rt) {
-          const int r0 = rt * 16 + g, r1 = r0 + 8;
-          float s0 = 1.0f, s1 = 1.0f, o0 = 0.0f, o1 = 0.0f;
-          if (GROUPED) {
-            const float2 p0 = so[gl * R + r0], p1 = so[gl * R + r1];
-            s0 = p0.x; o0 = p0.y;
-            s1 = p1.x; o1 = p1.y;
-          }
-          uint32_t a0[8], a1[8];
-          load_a<FMT>(stage + r0 * F::kRowStride, t, a0);
-          load_a<FMT>(stage + r1 * F::kRowStride, t, a1);
-          if (GROUPED) {
-            float tmp[MB][4];
-#pragma unroll
-            for (int mb = 0; mb < MB; ++mb) {
-              tmp[mb][0] = tmp[mb][1] = tmp[mb][2] = tmp[mb][3] = 0.0f;
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                mma_bf16_16816(tmp[mb], a0[2 * i], a1[2 * i], a0[2 * i + 1], a1[2 * i + 1], xf[mb][2 * i],
-                               xf[mb][2 * i + 1]);
-              if (F::kBits == 4) {
-                acc[rt][mb][0] += fmaf(s0, tmp[mb][0], o0 * xs2[mb][0]);
-                acc[rt][mb][1] += fmaf(s0, tmp[mb][1], o0 * xs2[mb][1]);
-                acc[rt][mb][2] += fmaf(s1, tmp[mb][2], o1 * xs2[mb][0]);
-                acc[rt][mb][3] += fmaf(s1, tmp[mb][3], o1 * xs2[mb][1]);
-              } else {
-                acc[rt][mb][0] = fmaf(s0, tmp[mb][0], acc[rt][mb][0]);
-                acc[rt][mb][1] = fmaf(s0, tmp[mb][1], acc[rt][mb][1]);
-                acc[rt][mb][2] = fmaf(s1, tmp[mb][2], acc[rt][mb][2]);
-                acc[rt][mb][3] = fmaf(s1, tmp[mb][3], acc[rt][mb][3]);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                mma_bf16_16816(acc[rt][mb], a0[2 * i], a1[2 * i], a0[2 * i + 1], a1[2 * i + 1], xf[mb][2 * i],
-                               xf[mb][2 * i + 1]);
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
-    }
-    // split-K inside the CTA: eight warps add into one [R][MP] tile
-#pragma unroll
-    for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-      for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = rt * 16 + g + ((i & 2) ? 8 : 0);
-          const int col = mb * 8 + 2 * t + (i & 1);
-          atomicAdd(&red[row * MP + col], acc[rt][mb][i]);
-        }
-  }
-  __syncthreads();
-
-  // ---- split-K across the cluster, then the epilogue -----------------------------
-  cg::cluster_group cluster = cg::this_cluster();
-  if (split > 1) cluster.sync();
-  const int rows_per_rank = (R + split - 1) / split;
-  const int r_begin = blockIdx.y * rows_per_rank;
-  const int r_end = min(min(r_begin + rows_per_rank, R), rows_valid);
-  const int r_count = r_end - r_begin;
-  if (r_count > 0) {
-    for (int idx = tid; idx < r_count * a.M; idx += kThreads) {
-      const int r = r_begin + idx % r_count;
-      const int m = idx / r_count;
-      float v;
-      if (split > 1) {
-        v = 0.0f;
-        for (int c = 0; c < split; ++c) v += cluster.map_shared_rank(red, c)[r * MP + m];
-      } else {
-        v = red[r * MP + m];
-      }
-      const int n = n0 + r;
-      if (!GROUPED && F::kBits != 16) v *= ldg_bf16(a.scale + n);
-      if (a.epilogue == kEpilogueGemm) {
-        const size_t o = static_cast<size_t>(m) * a.out_vec_stride + static_cast<size_t>(n) * a.out_row_stride;
-        v *= a.alpha;
-        const int bi = a.bias_by_vec ? m : n;
-        if (a.out_f32) {
-          if (a.gemm_bias != nullptr) v += static_cast<const float*>(a.gemm_bias)[bi];
-          if (a.aux != nullptr) static_cast<float*>(a.aux)[o] = v;
-          static_cast<float*>(a.out)[o] = apply_act(a.act, v);
+      for (int mb = 0; mb < MB; ++mb) {
+        const int m = mb * 8 + g;
+        if (m < a.M) {
+          const uint4 v0 = xs[((gl * 2 + 0) * a.M + m) * 4 + t];
+          const uint4 v1 = xs[((gl * 2 + 1) * a.M + m) * 4 + t];
+          xf[mb][0] = v0.x; xf[mb][1] = v0.y; xf[mb][2] = v0.z; xf[mb][3] = v0.w;
+          xf[mb][4] = v1.x; xf[mb][5] = v1.y; xf[mb][6] = v1.z; xf[mb][7] = v1.w;
         } else {
-          if (a.gemm_bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(a.gemm_bias)[bi]);
-          if (a.aux != nullptr) static_cast<__nv_bfloat16*>(a.aux)[o] = __float2bfloat16_rn(v);
-          static_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(apply_act(a.act, v));
+#pragma unroll
+          for (int r = 0; r < 8; ++r) xf[mb][r] = 0u;
         }
-        continue;
+        xs2[mb][0] = xs2[mb][1] = 0.0f;
+        if (F::kBits == 4) {
+          const float2 v = *reinterpret_cast<const float2*>(&xsum[gl * MP + mb * 8 + 2 * t]);
+          xs2[mb][0] = v.x;
+          xs2[mb][1] = v.y;
+        }
       }
-      const float y = bf16_round(v);
-      const size_t o = static_cast<size_t>(m) * a.ldo + n;
-      if (a.epilogue == B200_QMM_OUT_F32_RAW) {
-        reinterpret_cast<float*>(a.out)[o] = v;
-      } else if (a.epilogue == B200_QMM_OUT_F32) {
-        reinterpret_cast<float*>(a.out)[o] = y;
-      } else if (a.epilogue == B200_QMM_ADD_RESIDUAL) {
-        reinterpret_cast<__nv_bfloat16*>(a.out)[o] =
-            __float2bfloat16_rn(__bfloat162float(a.residual[o]) + y);
+    };
+    // one group (64 inputs) of every row tile: widen, multiply, scale, accumulate
+    auto do_group = [&](const uint8_t* stage_group, const float2* so_group, const uint32_t (&xf)[MB][8],
+                        const float (&xs2)[MB][2]) {
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        const int r0 = rt * 16 + g, r1 = r0 + 8;
+        uint32_t a0[8], a1[8];
+        load_a<FMT>(stage_group + r0 * kRowStride, t, a0);
+        load_a<FMT>(stage_group + r1 * kRowStride, t, a1);
+        if (GROUPED) {
+          const float2 p0 = so_group[r0], p1 = so_group[r1];
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb) {
+            float tmp[4];
+            mma_bf16_16816_z(tmp, a0[0], a1[0], a0[1], a1[1], xf[mb][0], xf[mb][1]);
+#pragma unroll
+            for (int i = 1; i < 4; ++i)
+              mma_bf16_16816(tmp, a0[2 * i], a1[2 * i], a0[2 * i + 1], a1[2 * i + 1], xf[mb][2 * i], xf[mb][2 * i + 1]);
+            if (F::kBits == 4) {
+              acc[rt][mb][0] = fmaf(p0.x, tmp[0], fmaf(p0.y, xs2[mb][0], acc[rt][mb][0]));
+              acc[rt][mb][1] = fmaf(p0.x, tmp[1], fmaf(p0.y, xs2[mb][1], acc[rt][mb][1]));
+              acc[rt][mb][2] = fmaf(p1.x, tmp[2], fmaf(p1.y, xs2[mb][0], acc[rt][mb][2]));
+              acc[rt][mb][3] = fmaf(p1.x, tmp[3], fmaf(p1.y, xs2[mb][1], acc[rt][mb][3]));
+            } else {
+              acc[rt][mb][0] = fmaf(p0.x, tmp[0], acc[rt][mb][0]);
+              acc[rt][mb][1] = fmaf(p0.x, tmp[1], acc[rt][mb][1]);
+              acc[rt][mb][2] = fmaf(p1.x, tmp[2], acc[rt][mb][2]);
+              acc[rt][mb][3] = fmaf(p1.x, tmp[3], acc[rt][mb][3]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              mma_bf16_16816(acc[rt][mb], a0[2 * i], a1[2 * i], a0[2 * i + 1], a1[2 * i + 1], xf[mb][2 * i],
+                             xf[mb][2 * i + 1]);
+        }
+      }
+    };
+
+    constexpr int GC = kChunkK / kGroupK;                       // groups per chunk
+    constexpr int GPW = KG > 0 ? KG / kConsumerWarps : 1;       // groups per warp (fast path)
+    uint32_t xr[GPW][MB][8];
+    float xq[GPW][MB][2];
+    if (KG > 0) {
+#pragma unroll
+      for (int j = 0; j < GPW; ++j) load_x(warp + kConsumerWarps * j, xr[j], xq[j]);
+    }
+
+    for (int ti = 0; ti < n_my; ++ti) {
+      const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
+      const int rows_valid = min(R, a.N - n0);
+      const float2* so_cur = so + (ti & 1) * so_buf;
+      float* red_cur = red + (ti & 1) * R * MP;
+      const bool has_next = ti + 1 < n_my;
+      if (has_next) scale_load(n0 + static_cast<int>(gridDim.x) * R);
+
+      if (KG > 0) {
+        // compile-time schedule: group j of this warp is warp + 16 j, in chunk (16 j) / GC
+        int s = 0;
+#pragma unroll
+        for (int j = 0; j < GPW; ++j) {
+          const int c = (kConsumerWarps * j) / GC;
+          const bool first = j == 0 || (kConsumerWarps * (j - 1)) / GC != c;
+          const bool last = j == GPW - 1 || (kConsumerWarps * (j + 1)) / GC != c;
+          if (first) {
+            const int u = ti * n_chunks + c;
+            s = u % NS;
+            if (!dead && !mbar_wait_bounded(&full[s], (u / NS) & 1)) {
+              report_timeout(a.status, 200 + s);
+              dead = true;
+            }
+          }
+          const int gs = warp + (kConsumerWarps * j) % GC;
+          if (!dead)
+            do_group(stage_base + static_cast<size_t>(s) * kStageBytes + gs * F::kGroupBytes,
+                     so_cur + (warp + kConsumerWarps * j) * R, xr[j], xq[j]);
+          if (last) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+          }
+        }
       } else {
-        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(v);
+        for (int c = 0; c < n_chunks; ++c) {
+          const int u = ti * n_chunks + c;
+          const int s = u % NS;
+          if (!dead && !mbar_wait_bounded(&full[s], (u / NS) & 1)) {
+            report_timeout(a.status, 200 + s);
+            dead = true;
+          }
+          const int chunk_groups = min(kChunkK, a.k_per_cta - c * kChunkK) / kGroupK;
+          for (int gs = warp; gs < chunk_groups && !dead; gs += kConsumerWarps) {
+            const int gl = c * GC + gs;     // group within this CTA's slice
+            uint32_t xf[MB][8];
+            float xs2[MB][2];
+            load_x(gl, xf, xs2);
+            do_group(stage_base + static_cast<size_t>(s) * kStageBytes + gs * F::kGroupBytes, so_cur + gl * R, xf, xs2);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+        }
+      }
+      // split-K inside the CTA: the warps add into one [R][MP] tile
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = rt * 16 + g + ((i & 2) ? 8 : 0);
+            const int col = mb * 8 + 2 * t + (i & 1);
+            atomicAdd(&red_cur[row * MP + col], acc[rt][mb][i]);
+            acc[rt][mb][i] = 0.0f;
+          }
+      if (has_next) scale_store(n0 + static_cast<int>(gridDim.x) * R, so + ((ti + 1) & 1) * so_buf);
+      if (persistent) {
+        consumer_barrier();
+        for (int idx = tid; idx < rows_valid * a.M; idx += kConsumerThreads) {
+          const int r = idx % rows_valid, m = idx / rows_valid;
+          const float v = red_cur[r * MP + m];
+          red_cur[r * MP + m] = 0.0f;   // this buffer is added into again two tiles from now
+          store_output<FMT, GROUPED>(a, v, m, n0 + r);
+        }
       }
     }
   }
-  if (split > 1) cluster.sync();  // peers may still be reading this CTA's tile
+  if (persistent) return;
+
+  // ---- split-K across the cluster (one tile per CTA), then the epilogue -----------------
+  __syncthreads();
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  {
+    const int n0 = static_cast<int>(blockIdx.x) * R;
+    const int rows_valid = min(R, a.N - n0);
+    const int rows_per_rank = (R + split - 1) / split;
+    const int r_begin = blockIdx.y * rows_per_rank;
+    const int r_end = min(min(r_begin + rows_per_rank, R), rows_valid);
+    const int r_count = r_end - r_begin;
+    if (r_count > 0) {
+      for (int idx = tid; idx < r_count * a.M; idx += kThreads) {
+        const int r = r_begin + idx % r_count;
+        const int m = idx / r_count;
+        float v = 0.0f;
+        for (int c = 0; c < split; ++c) v += cluster.map_shared_rank(red, c)[r * MP + m];
+        store_output<FMT, GROUPED>(a, v, m, n0 + r);
+      }
+    }
+  }
+  cluster.sync();  // peers may still be reading this CTA's tile
 }
 
 // ---------------------------------------------------------------------------
@@ -487,27 +605,23 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
 // ---------------------------------------------------------------------------
 
 struct Plan {
-  int fmt = 0, mb = 1, rt = 1, split = 1, stages = 2;
+  int fmt = 0, mb = 1, rt = 1, split = 1, stages = 2, tiles = 0, grid_x = 0;
   bool grouped = true;
   size_t smem = 0;
 };
 
-int ChunkRowStride(int fmt) {
-  switch (fmt) {
-    case kInt8: return Fmt<kInt8>::kRowStride;
-    case kBf16: return Fmt<kBf16>::kRowStride;
-    default: return Fmt<kInt4Seq>::kRowStride;
-  }
-}
+int BitsOf(int fmt) { return fmt == kInt8 ? 8 : (fmt == kBf16 ? 16 : 4); }
+int ChunkRowStride(int fmt, int rt) { return kCopyBytes / rt + (BitsOf(fmt) == 4 ? 32 : 64); }
+int ChunkK(int fmt, int rt) { return kCopyBytes / rt * 8 / BitsOf(fmt); }
 
 size_t SmemFor(const Plan& pl, int M, int k_per_cta) {
   const int R = 16 * pl.rt, MP = 8 * pl.mb, groups = k_per_cta / kGroupK;
   size_t off = (static_cast<size_t>(2 * pl.stages) * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(R) * MP * 4;
+  off += static_cast<size_t>(2) * R * MP * 4;
   off += (static_cast<size_t>(groups) * MP * 4 + 127) & ~static_cast<size_t>(127);
   off += (static_cast<size_t>(groups) * M * 128 + 127) & ~static_cast<size_t>(127);
-  if (pl.grouped) off += (static_cast<size_t>(groups) * R * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(pl.stages) * R * ChunkRowStride(pl.fmt);
+  if (pl.grouped) off += (static_cast<size_t>(2) * groups * R * 8 + 127) & ~static_cast<size_t>(127);
+  off += static_cast<size_t>(pl.stages) * R * ChunkRowStride(pl.fmt, pl.rt);
   return off;
 }
 
@@ -554,44 +668,44 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   pl.grouped = (p->bits == 4) || (p->bits == 8 && p->group == 64);
   const int M = static_cast<int>(p->M), N = static_cast<int>(p->N), K = static_cast<int>(p->K);
   pl.mb = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-  // More rows per CTA amortise the staging of x (read once per CTA from L2):
-  // keep x traffic at or below the weight traffic where the grid still fills.
-  const int rt_max = pl.mb == 4 ? 4 : (pl.mb == 2 ? 4 : (M <= 2 ? 1 : (M <= 4 ? 2 : 4)));
-  const int rt_min = pl.mb == 4 ? 4 : (pl.mb == 2 ? 2 : 1);
-  const int target = sm_count * 3 / 2;
+  // x is staged once per (persistent) CTA, so the tile height only has to give
+  // the x fragments some register reuse at larger batches.
+  pl.rt = pl.mb;
+  pl.tiles = static_cast<int>(CeilDiv(N, 16 * pl.rt));
+  // K is split across a cluster only when the row tiles alone cannot occupy the
+  // GPU, or when a CTA's slice of x would not fit shared memory.
   const size_t x_budget = 96 * 1024;
   bool found = false;
-  for (int rt = rt_max; rt >= rt_min && !found; rt >>= 1) {
-    const int tiles = static_cast<int>(CeilDiv(N, 16 * rt));
-    for (int split = 1; split <= 8; split <<= 1) {
-      if (K % (split * kGroupK) != 0) break;
-      const int kc = K / split;
-      if (static_cast<size_t>(M) * kc * 2 > x_budget) continue;
-      const bool fills = static_cast<int64_t>(tiles) * split >= target;
-      const bool last = split == 8 || K % (2 * split * kGroupK) != 0;
-      if (fills || (last && rt == rt_min)) {
-        pl.rt = rt;
-        pl.split = split;
-        found = true;
-        break;
-      }
+  for (int split = 1; split <= 8; split <<= 1) {
+    if (K % (split * kGroupK) != 0) break;
+    const int kc = K / split;
+    if (static_cast<size_t>(M) * kc * 2 > x_budget) continue;
+    const bool fills = static_cast<int64_t>(pl.tiles) * split >= sm_count;
+    const bool last = split == 8 || K % (2 * split * kGroupK) != 0;
+    if (fills || last) {
+      pl.split = split;
+      found = true;
+      break;
     }
   }
   if (!found)
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: M=%d K=%d does not fit the shared-memory staging of x", M, K);
   const int kc = K / pl.split;
-  const int chunks = static_cast<int>(CeilDiv(kc, kChunkK));
-  // Ring depth: everything in flight if it fits ~100 KB, else what fits.
-  const size_t budget = 100 * 1024;
-  pl.stages = chunks < 2 ? 2 : chunks;
+  const int chunks = static_cast<int>(CeilDiv(kc, ChunkK(pl.fmt, pl.rt)));
+  // One persistent CTA per SM (it walks tiles blockIdx.x, + grid, ...) with a deep
+  // ring: under load a bulk copy takes ~3 us to land, so ~6.5 TB/s needs well
+  // over 100 KB in flight per SM.
+  const int ctas_per_sm = 1;
+  pl.grid_x = pl.split > 1 ? pl.tiles : std::min(pl.tiles, sm_count * ctas_per_sm);
+  const int units = chunks * static_cast<int>(CeilDiv(pl.tiles, pl.grid_x));
+  // Ring depth: as many stages as the CTA has units, within ~200 KB.
+  const size_t budget = 200 * 1024;
+  pl.stages = std::min(units, 12);
+  const int min_stages = units < 2 ? 1 : 2;
   for (;;) {
     pl.smem = SmemFor(pl, M, kc);
-    if (pl.smem <= budget || pl.stages <= 2) break;
+    if (pl.smem <= budget || pl.stages <= min_stages) break;
     --pl.stages;
-  }
-  if (pl.stages > 32) {
-    pl.stages = 32;
-    pl.smem = SmemFor(pl, M, kc);
   }
   if (pl.smem > static_cast<size_t>(max_smem))
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: needs %zu bytes of shared memory (limit %d)", pl.smem, max_smem);
@@ -599,9 +713,9 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   return B200_OK;
 }
 
-template <int FMT, int MB, int RT, bool GROUPED>
+template <int FMT, int MB, int RT, bool GROUPED, int KG>
 cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
-  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED>;
+  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
   if (e != cudaSuccess) return e;
   LaunchCfg lc;
@@ -617,12 +731,12 @@ cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
 template <int FMT, bool GROUPED>
 cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
   switch (pl.mb * 10 + pl.rt) {
-    case 11: return LaunchOne<FMT, 1, 1, GROUPED>(pl, args, grid, stream);
-    case 12: return LaunchOne<FMT, 1, 2, GROUPED>(pl, args, grid, stream);
-    case 14: return LaunchOne<FMT, 1, 4, GROUPED>(pl, args, grid, stream);
-    case 22: return LaunchOne<FMT, 2, 2, GROUPED>(pl, args, grid, stream);
-    case 24: return LaunchOne<FMT, 2, 4, GROUPED>(pl, args, grid, stream);
-    case 44: return LaunchOne<FMT, 4, 4, GROUPED>(pl, args, grid, stream);
+    case 11:
+      // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
+      if (args.k_per_cta == 64 * kGroupK) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
+      return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
+    case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
+    case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -675,7 +789,8 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
   a.out_f32 = out_f32;
   a.gemm_bias = bias;
   a.aux = aux;
-  const dim3 grid(static_cast<unsigned>(CeilDiv(a.N, 16 * pl.rt)), pl.split, 1);
+  a.tiles = pl.tiles;
+  const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e = LaunchFmt<kBf16, false>(pl, a, grid, stream);
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "few-row GEMM launch: %s", cudaGetErrorString(e)));
   return EndLaunch(ctx, "b200_gemm (few-row)");
@@ -726,6 +841,8 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   a.x_vec = Aligned(p->x, 16) && a.ldx % 8 == 0 && (p->prologue != B200_QMM_PRO_RMSNORM || Aligned(p->prologue_gain, 16));
   a.scale_ld = p->bits == 16 ? 0 : static_cast<int>(p->K / p->group);
   a.k_per_cta = a.K / pl.split;
+  a.scale_vec = pl.grouped && (a.k_per_cta / kGroupK) % 8 == 0 && a.scale_ld % 8 == 0 && Aligned(p->scale, 16) &&
+                (p->bits != 4 || Aligned(p->bias, 16));
   a.epilogue = p->epilogue;
   a.stages = pl.stages;
   a.status = ctx->dev_status;
@@ -734,7 +851,8 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   a.act = a.bias_by_vec = a.out_f32 = 0;
   a.gemm_bias = nullptr;
   a.aux = nullptr;
-  const dim3 grid(static_cast<unsigned>(CeilDiv(a.N, 16 * pl.rt)), pl.split, 1);
+  a.tiles = pl.tiles;
+  const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e;
   switch (pl.fmt) {
     case kInt4Seq: e = LaunchFmt<kInt4Seq, true>(pl, a, grid, stream); break;

@@ -30,11 +30,21 @@ def peaks():
         return 6650.0, 1590.0, "fallback"
 
 
-def timed(fn, reps, warmup=3):
+def timed(fn, reps, warmup=3, graph=True):
+    """Seconds per call of fn.  With graph=True the launches of one call are
+    captured into a CUDA graph first, so the figure is device time, not the
+    host's launch rate."""
     import torch
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        eager, fn = fn, g.replay
+        fn()
+        torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(reps):

@@ -125,12 +125,12 @@ def test_qmm_validate_and_plan():
     assert v(q(ptr=None)) == L.INVALID_ARGUMENT
     assert v(q(ptr=4100)) == L.INVALID_ARGUMENT     # packed weights must be 16-byte aligned
     assert v(q(epi=1)) == L.INVALID_ARGUMENT        # residual epilogue without a residual
-    # plans: rows per CTA grow with the batch; small matrices split K across a cluster
+    # plans: tiles grow with the batch block count; small matrices split K across a cluster
     plan = p.qwen3.qmm_plan
     assert plan(1, 4096, 4096) == (16, 1, 1)
     assert plan(1, 1024, 4096)[1] >= 4
-    r8, s8, mb8 = plan(8, 4096, 4096)
-    assert mb8 == 1 and r8 >= 32 and r8 * s8 > 0
+    assert plan(8, 4096, 4096) == (16, 1, 1)        # persistent CTAs stage x once: no need for taller tiles
+    assert plan(16, 4096, 4096)[0] == 32 and plan(16, 4096, 4096)[2] == 2
     r32, s32, mb32 = plan(32, 4096, 12288)
     assert mb32 == 4 and 32 * (12288 // s32) * 2 <= 96 * 1024
 
