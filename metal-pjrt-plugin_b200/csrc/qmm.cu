@@ -24,6 +24,8 @@
 //     across CTAs through a thread-block cluster's distributed shared memory.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -87,6 +89,7 @@ struct QmmArgs {
   int x_vec;                   // x rows allow 16-byte loads
   int scale_vec;               // scale / offset rows allow 16-byte loads of eight groups
   int tiles;                   // row tiles in all (ceil(N / (16 RT)))
+  int dbg;                     // TEMP experiment mask
   float eps;
   const __nv_bfloat16* gain;   // RMSNorm gain [K]
 };
@@ -99,6 +102,12 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
   return d;
 }
 
+__device__ __forceinline__ uint32_t mulhi_shift(uint32_t v, uint32_t pow2) {
+  uint32_t d;
+  asm("mul.hi.u32 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(pow2));
+  return d;
+}
+
 // Widens one thread's share of a group (for one weight row) into 8 bf16x2 registers.
 template <int FMT>
 __device__ __forceinline__ void load_a(const uint8_t* row_group_ptr, int t, uint32_t (&a)[8]) {
@@ -106,8 +115,10 @@ __device__ __forceinline__ void load_a(const uint8_t* row_group_ptr, int t, uint
     const uint2 w = *reinterpret_cast<const uint2*>(row_group_ptr + 8 * t);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      a[r] = lop3_and_or(w.x >> (4 * r), 0x000f000fu, 0x43004300u);      // bf16 (128 + q)
-      a[4 + r] = lop3_and_or(w.y >> (4 * r), 0x000f000fu, 0x43004300u);
+      // the right shifts are multiply-high by a power of two: that instruction runs on the
+      // FMA pipe, which leaves the (half-rate) integer pipe to the lop3s
+      a[r] = lop3_and_or(r == 0 ? w.x : mulhi_shift(w.x, 1u << (32 - 4 * r)), 0x000f000fu, 0x43004300u);  // bf16 (128 + q)
+      a[4 + r] = lop3_and_or(r == 0 ? w.y : mulhi_shift(w.y, 1u << (32 - 4 * r)), 0x000f000fu, 0x43004300u);
     }
   } else if (FMT == kInt8) {
     const uint4 w = *reinterpret_cast<const uint4*>(row_group_ptr + 16 * t);
@@ -207,8 +218,13 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + NS;
   size_t off = (static_cast<size_t>(2 * NS) * 8 + 127) & ~static_cast<size_t>(127);
-  float* red = reinterpret_cast<float*>(smem + off);                 // [2][R][MP]
-  off += static_cast<size_t>(2) * R * MP * 4;
+  // Cross-warp reduction buffer.  Small tiles (one MMA row tile, batch <= 8) in a
+  // persistent CTA: every warp stores its partial tile, [2][warps][R][MP], and the
+  // epilogue threads add the 16 partials.  Otherwise: [2][R][MP] added into atomically.
+  constexpr bool kPartials = MB == 1 && RT == 1;
+  const bool partials = kPartials && persistent;
+  float* red = reinterpret_cast<float*>(smem + off);
+  off += static_cast<size_t>(2) * R * MP * 4 * (kPartials ? kConsumerWarps : 1);
   float* xsum = reinterpret_cast<float*>(smem + off);                // [groups_cta][MP]
   off += (static_cast<size_t>(groups_cta) * MP * 4 + 127) & ~static_cast<size_t>(127);
   uint4* xs = reinterpret_cast<uint4*>(smem + off);                  // [groups_cta][2][M][4] x 16 B
@@ -227,7 +243,8 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
     }
     mbar_fence_init();
   }
-  for (int i = tid; i < 2 * R * MP; i += kThreads) red[i] = 0.0f;
+  if (!partials)
+    for (int i = tid; i < 2 * R * MP; i += kThreads) red[i] = 0.0f;
   for (int i = tid; i < groups_cta * MP; i += kThreads) xsum[i] = 0.0f;
   __syncthreads();
 
@@ -501,9 +518,9 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
       const int rows_valid = min(R, a.N - n0);
       const float2* so_cur = so + (ti & 1) * so_buf;
-      float* red_cur = red + (ti & 1) * R * MP;
+      float* red_cur = red + (ti & 1) * R * MP * (partials ? kConsumerWarps : 1);
       const bool has_next = ti + 1 < n_my;
-      if (has_next) scale_load(n0 + static_cast<int>(gridDim.x) * R);
+      if (has_next && !(a.dbg & 4)) scale_load(n0 + static_cast<int>(gridDim.x) * R);
 
       if (KG > 0) {
         // compile-time schedule: group j of this warp is warp + 16 j, in chunk (16 j) / GC
@@ -522,7 +539,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
             }
           }
           const int gs = warp + (kConsumerWarps * j) % GC;
-          if (!dead)
+          if (!dead && !(a.dbg & 1))
             do_group(stage_base + static_cast<size_t>(s) * kStageBytes + gs * F::kGroupBytes,
                      so_cur + (warp + kConsumerWarps * j) * R, xr[j], xq[j]);
           if (last) {
@@ -550,26 +567,46 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
           if (lane == 0) mbar_arrive(&empty[s]);
         }
       }
-      // split-K inside the CTA: the warps add into one [R][MP] tile
+      // split-K inside the CTA
+      if (partials) {
+        // plain stores of this warp's partial tile: lane (g, t) holds rows g, g+8, columns 2t, 2t+1
+        float* mine = red_cur + warp * R * MP;
+        *reinterpret_cast<float2*>(&mine[g * MP + 2 * t]) = make_float2(acc[0][0][0], acc[0][0][1]);
+        *reinterpret_cast<float2*>(&mine[(g + 8) * MP + 2 * t]) = make_float2(acc[0][0][2], acc[0][0][3]);
+        acc[0][0][0] = acc[0][0][1] = acc[0][0][2] = acc[0][0][3] = 0.0f;
+      } else {
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt)
+        for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
+          for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int row = rt * 16 + g + ((i & 2) ? 8 : 0);
-            const int col = mb * 8 + 2 * t + (i & 1);
-            atomicAdd(&red_cur[row * MP + col], acc[rt][mb][i]);
-            acc[rt][mb][i] = 0.0f;
-          }
-      if (has_next) scale_store(n0 + static_cast<int>(gridDim.x) * R, so + ((ti + 1) & 1) * so_buf);
-      if (persistent) {
+            for (int i = 0; i < 4; ++i) {
+              const int row = rt * 16 + g + ((i & 2) ? 8 : 0);
+              const int col = mb * 8 + 2 * t + (i & 1);
+              atomicAdd(&red_cur[row * MP + col], acc[rt][mb][i]);
+              acc[rt][mb][i] = 0.0f;
+            }
+      }
+      if (has_next && !(a.dbg & 4)) scale_store(n0 + static_cast<int>(gridDim.x) * R, so + ((ti + 1) & 1) * so_buf);
+      if (persistent && !(a.dbg & 8)) {
         consumer_barrier();
-        for (int idx = tid; idx < rows_valid * a.M; idx += kConsumerThreads) {
-          const int r = idx % rows_valid, m = idx / rows_valid;
-          const float v = red_cur[r * MP + m];
-          red_cur[r * MP + m] = 0.0f;   // this buffer is added into again two tiles from now
-          store_output<FMT, GROUPED>(a, v, m, n0 + r);
+        if (partials) {
+          // the epilogue moves to other warps every tile, so no warp is always the late one
+          const int et = (tid + kConsumerThreads - ((ti * 128) % kConsumerThreads)) % kConsumerThreads;
+          if (et < rows_valid * a.M) {
+            const int r = et % rows_valid, m = et / rows_valid;
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) v += red_cur[(w * R + r) * MP + m];
+            store_output<FMT, GROUPED>(a, v, m, n0 + r);
+          }
+        } else {
+          for (int idx = tid; idx < rows_valid * a.M; idx += kConsumerThreads) {
+            const int r = idx % rows_valid, m = idx / rows_valid;
+            const float v = red_cur[r * MP + m];
+            red_cur[r * MP + m] = 0.0f;   // this buffer is added into again two tiles from now
+            store_output<FMT, GROUPED>(a, v, m, n0 + r);
+          }
         }
       }
     }
@@ -617,7 +654,7 @@ int ChunkK(int fmt, int rt) { return kCopyBytes / rt * 8 / BitsOf(fmt); }
 size_t SmemFor(const Plan& pl, int M, int k_per_cta) {
   const int R = 16 * pl.rt, MP = 8 * pl.mb, groups = k_per_cta / kGroupK;
   size_t off = (static_cast<size_t>(2 * pl.stages) * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(2) * R * MP * 4;
+  off += static_cast<size_t>(2) * R * MP * 4 * ((pl.mb == 1 && pl.rt == 1) ? kConsumerWarps : 1);
   off += (static_cast<size_t>(groups) * MP * 4 + 127) & ~static_cast<size_t>(127);
   off += (static_cast<size_t>(groups) * M * 128 + 127) & ~static_cast<size_t>(127);
   if (pl.grouped) off += (static_cast<size_t>(2) * groups * R * 8 + 127) & ~static_cast<size_t>(127);
@@ -695,17 +732,22 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   // One persistent CTA per SM (it walks tiles blockIdx.x, + grid, ...) with a deep
   // ring: under load a bulk copy takes ~3 us to land, so ~6.5 TB/s needs well
   // over 100 KB in flight per SM.
-  const int ctas_per_sm = 1;
+  int ctas_per_sm = 1;
+  if (const char* f = std::getenv("B200_QMM_CTAS")) ctas_per_sm = std::max(1, atoi(f));   // TEMP experiment
   pl.grid_x = pl.split > 1 ? pl.tiles : std::min(pl.tiles, sm_count * ctas_per_sm);
   const int units = chunks * static_cast<int>(CeilDiv(pl.tiles, pl.grid_x));
   // Ring depth: as many stages as the CTA has units, within ~200 KB.
-  const size_t budget = 200 * 1024;
+  const size_t budget = ctas_per_sm == 1 ? 200 * 1024 : 110 * 1024;
   pl.stages = std::min(units, 12);
   const int min_stages = units < 2 ? 1 : 2;
   for (;;) {
     pl.smem = SmemFor(pl, M, kc);
     if (pl.smem <= budget || pl.stages <= min_stages) break;
     --pl.stages;
+  }
+  if (const char* f = std::getenv("B200_QMM_STAGES")) {   // TEMP experiment
+    pl.stages = std::max(1, atoi(f));
+    pl.smem = SmemFor(pl, M, kc);
   }
   if (pl.smem > static_cast<size_t>(max_smem))
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: needs %zu bytes of shared memory (limit %d)", pl.smem, max_smem);
@@ -733,7 +775,7 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
   switch (pl.mb * 10 + pl.rt) {
     case 11:
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
-      if (args.k_per_cta == 64 * kGroupK) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
+      if (args.k_per_cta == 64 * kGroupK && !std::getenv("B200_QMM_NOKG")) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
     case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
@@ -790,6 +832,7 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
   a.gemm_bias = bias;
   a.aux = aux;
   a.tiles = pl.tiles;
+  { const char* d = std::getenv("B200_QMM_DEBUG"); a.dbg = d ? atoi(d) : 0; }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e = LaunchFmt<kBf16, false>(pl, a, grid, stream);
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "few-row GEMM launch: %s", cudaGetErrorString(e)));
@@ -852,6 +895,7 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   a.gemm_bias = nullptr;
   a.aux = nullptr;
   a.tiles = pl.tiles;
+  { const char* d = std::getenv("B200_QMM_DEBUG"); a.dbg = d ? atoi(d) : 0; }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e;
   switch (pl.fmt) {
