@@ -142,3 +142,93 @@ def test_config2_bias_silu(m):
     v = a.astype(np.float64) @ b.astype(np.float64) + bias.astype(np.float64)
     want = dense.act(3, v)
     assert dense.max_abs_over_rms(d, want) <= 2e-2
+
+
+# ---- the tensor-core (tcgen05) route -------------------------------------------------------
+
+def _tc_case(m, n, k, ta=False, tb=False, dt_in="bf16", dt_out=None, alpha=1.0, beta=0.0, act=0, bias=False,
+             aux=False, seed=0):
+    """Like run_case but with 16-byte-aligned leading dimensions, asserting the route."""
+    import torch
+    p = pkg()
+    dt_out = dt_out or dt_in
+    rng = np.random.default_rng(seed)
+    r8 = lambda v: (v + 7) // 8 * 8
+    ar, ac = (k, m) if ta else (m, k)
+    br, bc = (n, k) if tb else (k, n)
+    lda, ldb, ldd = r8(ac), r8(bc), r8(n) + 8
+    A = rng.standard_normal((ar, lda)).astype(NP[dt_in])
+    B = (rng.standard_normal((br, ldb)) * 0.5).astype(NP[dt_in])
+    D0 = rng.standard_normal((m, ldd)).astype(NP[dt_out])
+    bias_h = rng.standard_normal((n,)).astype(NP[dt_out]) if bias else None
+    At, Bt, Dt = dev(A), dev(B), dev(D0)
+    aux_t = torch.full_like(Dt, 7.0) if aux else None
+    bias_t = dev(bias_h) if bias else None
+    B_ = p.blas
+    prm = B_.GemmParams(m, n, k, B_.Operand(At, lda, 0, ta), B_.Operand(Bt, ldb, 0, tb), B_.Operand(Dt, ldd), 1, alpha, beta)
+    epi = B_.SteelEpilogue(act, bias_t, aux_t)
+    # few-row x . W^T shapes prefer the streaming kernel; force the tensor-core route here
+    assert B_.gemm_route(prm, epi) in (p._lib.ROUTE_TCGEN05, p._lib.ROUTE_FEWROW)
+    B_.run_steel_gemm(prm, epi, route=p._lib.ROUTE_TCGEN05)
+    torch.cuda.synchronize()
+    assert p.default_context().error() == 0
+    a_log, b_log = A[:, :ac].astype(np.float64), B[:, :bc].astype(np.float64)
+    if ta:
+        a_log = a_log.T
+    if tb:
+        b_log = b_log.T
+    v = alpha * (a_log @ b_log)
+    mag = abs(alpha) * (np.abs(a_log) @ np.abs(b_log))
+    if beta != 0:
+        v = v + beta * D0[:, :n].astype(np.float64)
+        mag = mag + np.abs(beta * D0[:, :n].astype(np.float64))
+    if bias:
+        v = v + bias_h.astype(np.float64)
+        mag = mag + np.abs(bias_h.astype(np.float64))
+    want = dense.act(act, v)
+    got = host(Dt).astype(np.float64)
+    tol = dense.tolerance(want, mag, k, NP[dt_out]) * 1.13
+    err = np.abs(got[:, :n] - want)
+    assert np.all(err <= tol), f"max err {err.max()} at {np.unravel_index(np.argmax(err - tol), err.shape)}"
+    assert np.array_equal(host(Dt)[:, n:].view(np.uint8), D0[:, n:].view(np.uint8))   # padding untouched
+    if aux:
+        ga = host(aux_t).astype(np.float64)
+        assert np.all(np.abs(ga[:, :n] - v) <= dense.tolerance(v, mag, k, NP[dt_out]) * 1.13)
+        assert np.all(ga[:, n:] == 7.0)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (256, 512, 320), (200, 264, 136), (33, 40, 72),
+                                   (1, 4096, 512), (300, 1000, 1024)])
+def test_tcgen05_layouts_and_ragged_edges(m, n, k, ta, tb):
+    _tc_case(m, n, k, ta=ta, tb=tb, seed=m + n)
+
+
+@pytest.mark.parametrize("dt_in,dt_out", [("bf16", "bf16"), ("f16", "f16"), ("bf16", "f32"), ("f16", "f32")])
+def test_tcgen05_dtypes_and_epilogues(dt_in, dt_out):
+    for act in (0, 1, 2, 3):
+        _tc_case(160, 288, 192, dt_in=dt_in, dt_out=dt_out, act=act, bias=True, aux=(act % 2 == 1), seed=act)
+    _tc_case(160, 288, 192, dt_in=dt_in, dt_out=dt_out, alpha=-0.5, beta=0.75)
+
+
+def test_tcgen05_many_tiles_persistent():
+    """More tiles than SMs, so every CTA walks several tiles and both accumulators rotate."""
+    _tc_case(2048, 2560, 256, bias=True, act=3)
+    _tc_case(1536, 4096, 512, tb=True)
+
+
+@pytest.mark.parametrize("m", [2048, 8192])
+def test_config2_large_m_properties(m):
+    """Config 2 at the sizes the CPU cannot check in full: a sample of rows against the
+    float64 oracle, and linearity in A (rows scaled by powers of two scale exactly)."""
+    import torch
+    p = pkg()
+    a, b, bias = inputs.config2(m)
+    ad, bd, biasd = dev(a), dev(b), dev(bias)
+    d = p.blas.matmul(ad, bd, bias=biasd, act=3)
+    rows = np.random.default_rng(0).choice(m, 24, replace=False)
+    v = a[rows].astype(np.float64) @ b.astype(np.float64) + bias.astype(np.float64)
+    assert dense.max_abs_over_rms(host(d)[rows].astype(np.float64), dense.act(3, v)) <= 2e-2
+    lin1 = p.blas.matmul(ad, bd)
+    lin2 = p.blas.matmul(ad * 2, bd)
+    assert torch.equal(lin2, lin1 * 2)
