@@ -254,6 +254,21 @@ size_t b200_attention_scratch_bytes(int64_t batch, int heads, int head_dim, int6
 b200_status b200_attention_decode(b200_context* ctx, b200_stream stream, const void* q, const void* k_cache,
                                   const void* v_cache, void* out, const int32_t* pos, void* scratch,
                                   int64_t batch, int heads, int kv_heads, int head_dim, int64_t max_len);
+/* The same attention for callers that cannot allocate device memory (no counterpart in
+ * the reference).  Who that is: a caller in the middle of a stream capture, where
+ * cudaMalloc is not allowed, or a plugin host whose own allocator has claimed the whole
+ * device and gives plugins no way to ask for more.  The partials go into an 8 MiB array
+ * that is part of the library image on every GPU that loads it, so there is no scratch
+ * argument and the call allocates nothing; a problem whose partials
+ * (b200_attention_scratch_bytes) exceed 8 MiB is refused with B200_RESOURCE_EXHAUSTED.
+ * The first call on a device looks up the array's device address (once per device);
+ * make that first call outside any stream capture.  All calls share the one array: it
+ * keeps whatever the last call left (nothing in it needs clearing, every value read is
+ * written first within the call), and two calls that overlap on the GPU - different
+ * streams, or different contexts on one device - race on it. */
+b200_status b200_attention_decode_static(b200_context* ctx, b200_stream stream, const void* q, const void* k_cache,
+                                         const void* v_cache, void* out, const int32_t* pos, int64_t batch,
+                                         int heads, int kv_heads, int head_dim, int64_t max_len);
 /* The fused form the decoder uses: per-head RMSNorm + RoPE of q and of the new k,
  * the cache writes of k and v at *pos, and attention over slots [0, *pos], all
  * from the fused projection row qkv bf16 [B, (H + 2 KV) * D] (qwen3.py:363-372).

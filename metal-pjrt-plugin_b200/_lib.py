@@ -98,6 +98,7 @@ PROTOTYPES = {
                                      C.c_float, C.c_float]),
     "b200_attention_scratch_bytes": (C.c_size_t, [_I64, _I, _I, _I64]),
     "b200_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64]),
+    "b200_attention_decode_static": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64]),
     "b200_attention_step": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64,
                                  C.c_float, C.c_float]),
     "b200_silu_mul": (_I, [_VP, _VP, _VP, _VP, _I64, _I64]),

@@ -13,6 +13,8 @@
 // RoPE of q from the fused qkv row, and - in the CTA whose slots contain the
 // new position - of k, plus the cache writes of k and v.  That CTA takes the
 // new key/value from shared memory, so nothing is read back after being written.
+#include <mutex>
+
 #include "common.cuh"
 
 using namespace b200;
@@ -346,6 +348,36 @@ b200_status Run(b200_context* ctx, cudaStream_t stream, AttnArgs a, const char* 
                          : LaunchAttn<64>(ctx, stream, a, a.heads / a.kv_heads, batch);
 }
 
+// ---- scratch that nobody has to allocate ------------------------------------------------
+// Some hosts of this library may not allocate device memory when they call it: code that
+// runs inside a stream capture, or a runtime whose allocator owns every byte of the device
+// and forbids cudaMalloc from plugins.  For them the split-attention partials can live in
+// this fixed array instead of a caller-provided buffer.  Every GPU that loads the library
+// carries it until the process exits.
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;   // 8 MiB
+static __device__ __align__(256) float g_attn_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mu;
+float* g_scratch_ptr[kMaxDevices] = {};   // device address of g_attn_scratch, per device ordinal
+
+// In host code `g_attn_scratch` is only a handle for the symbol, not a device address, so
+// the address is asked for once per device (with that device current) and cached.
+b200_status StaticScratch(b200_context* ctx, float** out) {
+  if (ctx->device < 0 || ctx->device >= kMaxDevices)
+    return Fail(B200_UNIMPLEMENTED, "b200_attention_decode_static: device ordinal %d beyond %d", ctx->device, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_ptr[ctx->device] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return Stick(ctx, Fail(B200_INTERNAL, "cudaGetSymbolAddress(static attention scratch): %s", cudaGetErrorString(e)));
+    g_scratch_ptr[ctx->device] = p;
+  }
+  *out = g_scratch_ptr[ctx->device];
+  return B200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -391,6 +423,36 @@ b200_status b200_attention_step(b200_context* ctx, b200_stream stream, const voi
   a.theta = theta;
   a.eps = eps;
   return Run(ctx, stream, a, "b200_attention_step", batch, head_dim);
+}
+
+b200_status b200_attention_decode_static(b200_context* ctx, b200_stream stream, const void* q, const void* k_cache,
+                                         const void* v_cache, void* out, const int32_t* pos, int64_t batch,
+                                         int heads, int kv_heads, int head_dim, int64_t max_len) {
+  b200_status s = BeginLaunch(ctx);   // makes the context's device current
+  if (s != B200_OK) return s;
+  if (batch < 0 || heads <= 0 || max_len <= 0 || (head_dim != 64 && head_dim != 128))
+    return Fail(B200_INVALID_ARGUMENT, "b200_attention_decode_static: bad sizes");
+  const size_t need = b200_attention_scratch_bytes(batch, heads, head_dim, max_len);
+  if (need > kStaticScratchFloats * sizeof(float))
+    return Fail(B200_RESOURCE_EXHAUSTED,
+                "b200_attention_decode_static: batch %lld x heads %d x max_len %lld needs %zu bytes of scratch; the "
+                "built-in scratch holds %zu (use b200_attention_decode with a caller buffer)",
+                static_cast<long long>(batch), heads, static_cast<long long>(max_len), need,
+                kStaticScratchFloats * sizeof(float));
+  float* scratch = nullptr;
+  s = StaticScratch(ctx, &scratch);
+  if (s != B200_OK) return s;
+  AttnArgs a = {};
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.k_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(k_cache));
+  a.v_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(v_cache));
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.pos = pos;
+  a.scratch = scratch;   // every partial the merge reads is written earlier in the same call: nothing to clear
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.max_len = max_len;
+  return Run(ctx, stream, a, "b200_attention_decode_static", batch, head_dim);
 }
 
 }  // extern "C"
