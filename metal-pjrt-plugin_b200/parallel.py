@@ -76,3 +76,42 @@ def gate_up_row_index(cfg, rank, world):
     inter = cfg["inter"]
     g = np.arange(inter).reshape(world, -1)[rank]
     return np.concatenate([g, inter + g])
+
+
+def _contig(a):
+    return a.contiguous() if hasattr(a, "contiguous") else __import__("numpy").ascontiguousarray(a)
+
+
+def _rows(w, idx):
+    if hasattr(idx, "dtype") and not isinstance(idx, slice) and hasattr(next(iter(w.values())), "device"):
+        import torch
+        idx = torch.as_tensor(idx, device=next(iter(w.values())).device)
+    return {k: _contig(v[idx]) for k, v in w.items()}
+
+
+def _cols(w, sl):
+    """Input columns [sl) of an int4 [N, K] weight: K/8 words and K/64 groups per row."""
+    return {"q4": _contig(w["q4"][:, sl.start // 8:sl.stop // 8]), "s": _contig(w["s"][:, sl.start // 64:sl.stop // 64]),
+            "b": _contig(w["b"][:, sl.start // 64:sl.stop // 64])}
+
+
+def shard_params(params, cache, cfg, rank, world):
+    """This rank's shard of a decoder pytree (NumPy or torch): qkv and gate_up by output
+    rows, o and down by input columns, the LM head by vocabulary rows, the KV cache by KV
+    head; norms and the embedding are replicated.  Returns (params, cache, local cfg)."""
+    local = local_config(cfg, world)
+    D = cfg["head_dim"]
+    hd = shard_rows(cfg["heads"] * D, rank, world)
+    it = shard_rows(cfg["inter"], rank, world)
+    kv = shard_rows(cfg["kv_heads"], rank, world)
+    layers = []
+    for lp in params["layers"]:
+        layers.append({"attn_norm": lp["attn_norm"], "q_norm": lp["q_norm"], "k_norm": lp["k_norm"],
+                       "mlp_norm": lp["mlp_norm"],
+                       "qkv": _rows(lp["qkv"], qkv_row_index(cfg, rank, world)), "o": _cols(lp["o"], hd),
+                       "gate_up": _rows(lp["gate_up"], gate_up_row_index(cfg, rank, world)),
+                       "down": _cols(lp["down"], it)})
+    out = {"embed": params["embed"], "norm": params["norm"], "layers": layers,
+           "lm_head": _contig(params["lm_head"][shard_rows(cfg["vocab"], rank, world)])}
+    lcache = {"k": [_contig(k[:, kv]) for k in cache["k"]], "v": [_contig(v[:, kv]) for v in cache["v"]]}
+    return out, lcache, local

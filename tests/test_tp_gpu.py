@@ -1,0 +1,76 @@
+"""Tensor-parallel decoder on 2 GPUs (one process per GPU, NCCL through the library)
+against the unsharded CPU oracle.  Skipped where fewer than two devices are visible.
+Ranks leave only after the step has been synchronised; NVLS is switched off for NCCL."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from util import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from oracle import decoder as odec
+    from oracle import dense, inputs
+    from util import dev, dev_params, host
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from metal_pjrt_plugin_b200 import parallel
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = pkg.Context(rank)
+    tp = parallel.TensorParallel.from_torch_distributed(ctx)
+    cfg = inputs.decoder_config(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=512, vocab=1024)
+    B, ctxlen, max_len = 3, 40, 64
+    params, cache, tokens = inputs.config5(cfg, B, ctxlen, max_len=max_len)
+    sp, sc, local = parallel.shard_params(params, cache, cfg, rank, world)
+    device = f"cuda:{rank}"
+    dp = dev_params(sp, device)
+    dc = {k: [dev(a, device) for a in v] for k, v in sc.items()}
+    dec = pkg.qwen3.Decoder(dp, dc, local, max_batch=B, ctx=ctx, tp=tp)
+    tok = dev(tokens.astype(np.int32), device)
+    pos = torch.tensor([ctxlen], dtype=torch.int32, device=device)
+    logits = dec.step(tok, pos)
+    logits2 = dec.step(tok, pos).clone()      # graph replay
+    torch.cuda.synchronize()
+    status = ctx.error()
+    got = host(logits)                                           # [world, B, V / world], rank-major
+    got = np.concatenate([got[r] for r in range(world)], axis=-1)
+    res = None
+    if rank == 0:
+        want = odec.decode_step(params, tokens, {k: [a.copy() for a in v] for k, v in cache.items()}, ctxlen, cfg)
+        res = (float(dense.max_abs_over_rms(got, want)), bool(np.array_equal(got.argmax(-1), want.argmax(-1))),
+               bool(torch.equal(logits, logits2)), int(status))
+    dist.barrier()
+    out_q.put((rank, res))
+    dec.close()
+    tp.close()
+    dist.destroy_process_group()
+
+
+def test_tp2_decoder_matches_oracle():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p_ in procs:
+        p_.start()
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p_ in procs:
+        p_.join(timeout=120)
+        assert p_.exitcode == 0
+    err, same_argmax, replay_equal, status = res[0]
+    assert status == 0
+    assert err <= 6e-2 and same_argmax and replay_equal
