@@ -191,7 +191,7 @@ def workload_config(batch, world):
 # GPU arm
 # ------------------------------------------------------------------------------------------
 
-def build_device_model(pkg, cfg_local, batch, device, seed, world, rank):
+def build_device_model(pkg, cfg_local, batch, device, seed, world, rank, ctx):
     """Random-init N(0, 0.02) weights quantised on the device (int4-g64), norms
     gain 1, bf16 embedding / LM head, cache of CTX prior tokens ~ N(0, 1)."""
     import torch
@@ -201,7 +201,7 @@ def build_device_model(pkg, cfg_local, batch, device, seed, world, rank):
 
     def qmat(n, k):
         w = torch.randn((n, k), generator=g, device=device, dtype=torch.float32).mul_(0.02)
-        q = pkg.qwen3.quantize_int4(w)
+        q = pkg.qwen3.quantize_int4(w, ctx=ctx)
         del w
         return q
     ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
@@ -223,7 +223,7 @@ def build_device_model(pkg, cfg_local, batch, device, seed, world, rank):
     return params, cache
 
 
-def time_projection_kernels(pkg, params, cfg_local, batch, device, reps):
+def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
     """The dequant-GEMV alone: every int4 projection of the model launched back
     to back over its own weights (4 x layers distinct buffers, far beyond L2)."""
     import torch
@@ -239,13 +239,13 @@ def time_projection_kernels(pkg, params, cfg_local, batch, device, reps):
             jobs.append((xs[k], w))
             nbytes += n * k * 0.5625 + 2 * batch * (k + n)
     for x, w in jobs[:8]:
-        pkg.qwen3.linear(x, w)
+        pkg.qwen3.linear(x, w, ctx=ctx)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(reps):
         for x, w in jobs:
-            pkg.qwen3.linear(x, w)
+            pkg.qwen3.linear(x, w, ctx=ctx)
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop)
@@ -273,7 +273,7 @@ def run_ours(args):
         tp = parallel.TensorParallel.from_torch_distributed(ctx)
         cfg_local = parallel.local_config(CFG, world)
     B = args.batch
-    params, cache = build_device_model(pkg, cfg_local, B, device, 4, world, rank)
+    params, cache = build_device_model(pkg, cfg_local, B, device, 4, world, rank, ctx)
     dec = pkg.qwen3.Decoder(params, cache, cfg_local, max_batch=B, ctx=ctx, tp=tp)
 
     tok_host = torch.randint(0, CFG["vocab"], (B,), dtype=torch.int32).pin_memory()
@@ -330,7 +330,7 @@ def run_ours(args):
 
     # ---- the dominant kernel alone ----------------------------------------------
     peak, peak_kind = measured_peaks()
-    bytes_per_launch, sec_per_launch, qlaunches = time_projection_kernels(pkg, params, cfg_local, B, device, reps=3)
+    bytes_per_launch, sec_per_launch, qlaunches = time_projection_kernels(pkg, params, cfg_local, B, device, reps=3, ctx=ctx)
     achieved = bytes_per_launch / sec_per_launch / 1e9
 
     if rank != 0:

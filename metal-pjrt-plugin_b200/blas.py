@@ -80,7 +80,7 @@ def gemm_work(p: GemmParams):
 def run_steel_gemm(p: GemmParams, epi: Optional[SteelEpilogue] = None, ctx=None, stream=None, route=0):
     """≙ RunSteelGemm / RunGemv: enqueue on the stream, return nothing, raise
     B200Error(INVALID_ARGUMENT / UNIMPLEMENTED / ...) like the absl::Status."""
-    ctx = ctx or default_context()
+    ctx = ctx or default_context(p.c.tensor.device.index or 0)
     pc = p.to_c()
     ec = (epi or SteelEpilogue()).to_c()
     L = _lib.lib()

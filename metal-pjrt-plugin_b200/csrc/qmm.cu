@@ -89,7 +89,6 @@ struct QmmArgs {
   int x_vec;                   // x rows allow 16-byte loads
   int scale_vec;               // scale / offset rows allow 16-byte loads of eight groups
   int tiles;                   // row tiles in all (ceil(N / (16 RT)))
-  int dbg;                     // TEMP experiment mask
   float eps;
   const __nv_bfloat16* gain;   // RMSNorm gain [K]
 };
@@ -520,7 +519,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       const float2* so_cur = so + (ti & 1) * so_buf;
       float* red_cur = red + (ti & 1) * R * MP * (partials ? kConsumerWarps : 1);
       const bool has_next = ti + 1 < n_my;
-      if (has_next && !(a.dbg & 4)) scale_load(n0 + static_cast<int>(gridDim.x) * R);
+      if (has_next) scale_load(n0 + static_cast<int>(gridDim.x) * R);
 
       if (KG > 0) {
         // compile-time schedule: group j of this warp is warp + 16 j, in chunk (16 j) / GC
@@ -539,7 +538,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
             }
           }
           const int gs = warp + (kConsumerWarps * j) % GC;
-          if (!dead && !(a.dbg & 1))
+          if (!dead)
             do_group(stage_base + static_cast<size_t>(s) * kStageBytes + gs * F::kGroupBytes,
                      so_cur + (warp + kConsumerWarps * j) * R, xr[j], xq[j]);
           if (last) {
@@ -587,8 +586,8 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
               acc[rt][mb][i] = 0.0f;
             }
       }
-      if (has_next && !(a.dbg & 4)) scale_store(n0 + static_cast<int>(gridDim.x) * R, so + ((ti + 1) & 1) * so_buf);
-      if (persistent && !(a.dbg & 8)) {
+      if (has_next) scale_store(n0 + static_cast<int>(gridDim.x) * R, so + ((ti + 1) & 1) * so_buf);
+      if (persistent) {
         consumer_barrier();
         if (partials) {
           // the epilogue moves to other warps every tile, so no warp is always the late one
@@ -732,22 +731,17 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   // One persistent CTA per SM (it walks tiles blockIdx.x, + grid, ...) with a deep
   // ring: under load a bulk copy takes ~3 us to land, so ~6.5 TB/s needs well
   // over 100 KB in flight per SM.
-  int ctas_per_sm = 1;
-  if (const char* f = std::getenv("B200_QMM_CTAS")) ctas_per_sm = std::max(1, atoi(f));   // TEMP experiment
+  const int ctas_per_sm = 1;
   pl.grid_x = pl.split > 1 ? pl.tiles : std::min(pl.tiles, sm_count * ctas_per_sm);
   const int units = chunks * static_cast<int>(CeilDiv(pl.tiles, pl.grid_x));
   // Ring depth: as many stages as the CTA has units, within ~200 KB.
-  const size_t budget = ctas_per_sm == 1 ? 200 * 1024 : 110 * 1024;
+  const size_t budget = 200 * 1024;
   pl.stages = std::min(units, 12);
   const int min_stages = units < 2 ? 1 : 2;
   for (;;) {
     pl.smem = SmemFor(pl, M, kc);
     if (pl.smem <= budget || pl.stages <= min_stages) break;
     --pl.stages;
-  }
-  if (const char* f = std::getenv("B200_QMM_STAGES")) {   // TEMP experiment
-    pl.stages = std::max(1, atoi(f));
-    pl.smem = SmemFor(pl, M, kc);
   }
   if (pl.smem > static_cast<size_t>(max_smem))
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: needs %zu bytes of shared memory (limit %d)", pl.smem, max_smem);
@@ -775,7 +769,7 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
   switch (pl.mb * 10 + pl.rt) {
     case 11:
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
-      if (args.k_per_cta == 64 * kGroupK && !std::getenv("B200_QMM_NOKG")) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
+      if (args.k_per_cta == 64 * kGroupK) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
     case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
@@ -832,7 +826,6 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
   a.gemm_bias = bias;
   a.aux = aux;
   a.tiles = pl.tiles;
-  { const char* d = std::getenv("B200_QMM_DEBUG"); a.dbg = d ? atoi(d) : 0; }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e = LaunchFmt<kBf16, false>(pl, a, grid, stream);
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "few-row GEMM launch: %s", cudaGetErrorString(e)));
@@ -895,7 +888,6 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   a.gemm_bias = nullptr;
   a.aux = nullptr;
   a.tiles = pl.tiles;
-  { const char* d = std::getenv("B200_QMM_DEBUG"); a.dbg = d ? atoi(d) : 0; }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e;
   switch (pl.fmt) {

@@ -9,7 +9,8 @@ from .context import default_context
 
 class TensorParallel:
     def __init__(self, rank, world, id_bytes, ctx=None):
-        self.ctx = ctx or default_context()
+        import torch
+        self.ctx = ctx or default_context(torch.cuda.current_device())
         self.rank, self.world = rank, world
         handle = C.c_void_p()
         buf = (C.c_char * _lib.TP_ID_BYTES).from_buffer_copy(id_bytes)

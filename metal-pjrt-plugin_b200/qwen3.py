@@ -27,7 +27,7 @@ def quantize_int4(w, group=GROUP, ctx=None):
     """≙ quantize_int4 (qwen3.py:169-196) in the benchmark's min/max variant,
     on the device. w: f32 or bf16 [N, K]."""
     torch = _torch()
-    ctx = ctx or default_context()
+    ctx = ctx or default_context(w.device.index or 0)
     N, K = w.shape
     w = w.contiguous()
     q = torch.empty((N, K // 8), dtype=torch.int32, device=w.device)
@@ -41,7 +41,7 @@ def quantize_int4(w, group=GROUP, ctx=None):
 def quantize_int8(w, group=None, ctx=None):
     """≙ quantize_int8 (qwen3.py:154-166); group None = one scale per output channel."""
     torch = _torch()
-    ctx = ctx or default_context()
+    ctx = ctx or default_context(w.device.index or 0)
     N, K = w.shape
     g = K if group is None else group
     w = w.contiguous()
@@ -71,8 +71,8 @@ def dequantize(w, dtype=None, ctx=None):
     """≙ dequantize (qwen3.py:199-207): the [out, in] matrix of a quantised
     weight, f32 (one rounding per operation) or bf16."""
     torch = _torch()
-    ctx = ctx or default_context()
     bits, group, order, q, s, b, N, K = _describe(w)
+    ctx = ctx or default_context(q.device.index or 0)
     dtype = dtype or torch.float32
     out = torch.empty((N, K), dtype=dtype, device=q.device)
     _lib.check(_lib.lib().b200_dequantize(ctx.handle, _lib.current_stream(), bits, group, order, _lib.ptr(q),
@@ -87,7 +87,7 @@ def linear(x, w, residual=None, out_f32=False, rms_gain=None, eps=1e-6, silu_mul
     f32 logits.  rms_gain fuses linear(rms_norm(x, rms_gain, eps), w) (up to 8
     rows); silu_mul fuses linear(silu(gate) * up, w) for x = [gate | up]."""
     torch = _torch()
-    ctx = ctx or default_context()
+    ctx = ctx or default_context(x.device.index or 0)
     bits, group, order, q, s, b, N, K = _describe(w)
     lead = x.shape[:-1]
     x2 = x.reshape(-1, 2 * K if silu_mul else K)
@@ -140,7 +140,7 @@ class Decoder:
     counts (see parallel.shard_params)."""
 
     def __init__(self, params, cache, cfg, max_batch, ctx=None, tp=None):
-        self.ctx = ctx or default_context()
+        self.ctx = ctx or default_context(params["embed"].device.index or 0)
         self.cfg, self.params, self.cache, self.tp = cfg, params, cache, tp
         L = cfg["layers"]
         max_len = cache["k"][0].shape[2]

@@ -9,7 +9,7 @@ KIND_RMS, KIND_SOFTMAX, KIND_LOG_SOFTMAX, KIND_LAYERNORM = 0, 1, 2, 3
 
 def rownorm(kind, x, gain=None, beta=None, eps=1e-6, out=None, ctx=None, stream=None):
     import torch
-    ctx = ctx or default_context()
+    ctx = ctx or default_context(x.device.index or 0)
     assert x.is_contiguous()
     n = x.shape[-1] if x.dim() else 0
     rows = x.numel() // n if n else 0
