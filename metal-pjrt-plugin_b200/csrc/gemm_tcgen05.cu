@@ -6,7 +6,7 @@
 // Structure (one persistent CTA per SM, 192 threads):
 //   warp 0    TMA producer: per K step one 128 x 64 tile of op(A) and one 64 x BN tile
 //             of op(B), as 128-byte-swizzled boxes of cp.async.bulk.tensor (no cluster
-//             multicast), into a 4-deep shared-memory ring guarded by mbarriers;
+//             multicast), into a 4- to 8-deep shared-memory ring guarded by mbarriers;
 //   warp 1    allocates tensor memory and issues tcgen05.mma (cta_group::1, kind::f16,
 //             M = 128, N = BN, K = 16) from shared-memory descriptors; tcgen05.commit
 //             releases ring slots and signals a finished accumulator;
@@ -29,7 +29,6 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;          // one 128-byte swizzle row of 16-bit elements
-constexpr int kStages = 4;
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 
@@ -117,6 +116,8 @@ struct Smem {
   static constexpr int kABytes = BM * BK * 2;        // 16 KB
   static constexpr int kBBytes = BN * BK * 2;        // 32 KB at BN = 256
   static constexpr int kStageBytes = kABytes + kBBytes;
+  // ~192 KB of ring whatever the tile width: narrow tiles stream B and need the depth
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kTotal = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
@@ -172,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a,
                    const uint32_t idesc) {
   using S = Smem<BN>;
+  constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
@@ -379,10 +381,10 @@ bool Tcgen05Supports(const b200_gemm_params* p, const b200_epilogue* epi) {
 b200_status RunTcgen05(b200_context* ctx, cudaStream_t stream, const b200_gemm_params* p, const b200_epilogue* epi) {
   const int ta = p->a.transpose, tb = p->b.transpose;
   const int64_t m = p->m, n = p->n, k = p->k;
-  // 128 x 256 tiles; 128 x 128 when that is what it takes to give every SM a tile
+  // 128 x 256 tiles; narrower ones (128, 64 columns) when that is what it takes to spread
+  // a few-row problem, which only streams B, over more SMs
   const int64_t tiles_m = CeilDiv(m, BM);
-  const bool wide = tiles_m * CeilDiv(n, 256) >= ctx->sm_count;
-  const int bn = wide ? 256 : 128;
+  const int bn = tiles_m * CeilDiv(n, 256) >= ctx->sm_count ? 256 : (tiles_m * CeilDiv(n, 128) >= ctx->sm_count ? 128 : 64);
   CUtensorMap ma, mb;
   bool ok;
   if (!ta) ok = MakeMap(&ma, p->a.dtype, p->a.ptr, k, m, p->a.ld, BK, BM);     // A [m][k]
@@ -416,10 +418,14 @@ b200_status RunTcgen05(b200_context* ctx, cudaStream_t stream, const b200_gemm_p
     if (out == B200_F32) e = LaunchTc<256, float>(ma, mb, a, idesc, grid, stream);
     else if (out == B200_BF16) e = LaunchTc<256, __nv_bfloat16>(ma, mb, a, idesc, grid, stream);
     else e = LaunchTc<256, __half>(ma, mb, a, idesc, grid, stream);
-  } else {
+  } else if (bn == 128) {
     if (out == B200_F32) e = LaunchTc<128, float>(ma, mb, a, idesc, grid, stream);
     else if (out == B200_BF16) e = LaunchTc<128, __nv_bfloat16>(ma, mb, a, idesc, grid, stream);
     else e = LaunchTc<128, __half>(ma, mb, a, idesc, grid, stream);
+  } else {
+    if (out == B200_F32) e = LaunchTc<64, float>(ma, mb, a, idesc, grid, stream);
+    else if (out == B200_BF16) e = LaunchTc<64, __nv_bfloat16>(ma, mb, a, idesc, grid, stream);
+    else e = LaunchTc<64, __half>(ma, mb, a, idesc, grid, stream);
   }
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "b200_gemm (tcgen05) launch: %s", cudaGetErrorString(e)));
   return EndLaunch(ctx, "b200_gemm (tcgen05)");
