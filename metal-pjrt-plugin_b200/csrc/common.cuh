@@ -167,15 +167,22 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // through the status word and leaves the pipeline.  The SM cycle counter is
 // read only after a few thousand failed polls (each poll may itself suspend the
 // thread for a while), so the common case costs nothing but the polls.
+// kSleepNs > 0 parks the warp between polls (a producer that is far ahead of its consumers
+// should not compete with them for issue slots).
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
-  for (int i = 0; i < 4096; ++i)
+  for (int i = 0; i < 4096; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
+  }
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 1024; ++i)
+    for (int i = 0; i < 1024; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (kSleepNs > 0) __nanosleep(kSleepNs);
+    }
     if (clock64() - t0 > 4000000000ll) return false;
   }
 }

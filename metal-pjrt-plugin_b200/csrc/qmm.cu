@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   constexpr int MP = 8 * MB;
   // One pipeline stage holds R rows x kChunkK inputs; a row's share arrives as ONE
   // bulk copy (small copies are bound by the copy engine's request rate, not by HBM).
-  constexpr int kChunkRowBytes = kCopyBytes / RT;
+  constexpr int kChunkRowBytes = MB == 1 ? kCopyBytes : kCopyBytes / RT;
   constexpr int kChunkK = kChunkRowBytes * 8 / F::kBits;
   constexpr int kRowStride = kChunkRowBytes + F::kPad;
   constexpr int kStageBytes = R * kRowStride;
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   // Cross-warp reduction buffer.  Small tiles (one MMA row tile, batch <= 8) in a
   // persistent CTA: every warp stores its partial tile, [2][warps][R][MP], and the
   // epilogue threads add the 16 partials.  Otherwise: [2][R][MP] added into atomically.
-  constexpr bool kPartials = MB == 1 && RT == 1;
+  constexpr bool kPartials = MB == 1;
   const bool partials = kPartials && persistent;
   float* red = reinterpret_cast<float*>(smem + off);
   off += static_cast<size_t>(2) * R * MP * 4 * (kPartials ? kConsumerWarps : 1);
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
       const int rows_valid = min(R, a.N - n0);
       const int s = u % NS, use = u / NS;
-      if (!dead && use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
+      if (!dead && use > 0 && !mbar_wait_bounded<128>(&empty[s], (use - 1) & 1)) {
         report_timeout(a.status, 100 + s);
         dead = true;
       }
@@ -570,9 +570,12 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       if (partials) {
         // plain stores of this warp's partial tile: lane (g, t) holds rows g, g+8, columns 2t, 2t+1
         float* mine = red_cur + warp * R * MP;
-        *reinterpret_cast<float2*>(&mine[g * MP + 2 * t]) = make_float2(acc[0][0][0], acc[0][0][1]);
-        *reinterpret_cast<float2*>(&mine[(g + 8) * MP + 2 * t]) = make_float2(acc[0][0][2], acc[0][0][3]);
-        acc[0][0][0] = acc[0][0][1] = acc[0][0][2] = acc[0][0][3] = 0.0f;
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+          *reinterpret_cast<float2*>(&mine[(rt * 16 + g) * MP + 2 * t]) = make_float2(acc[rt][0][0], acc[rt][0][1]);
+          *reinterpret_cast<float2*>(&mine[(rt * 16 + g + 8) * MP + 2 * t]) = make_float2(acc[rt][0][2], acc[rt][0][3]);
+          acc[rt][0][0] = acc[rt][0][1] = acc[rt][0][2] = acc[rt][0][3] = 0.0f;
+        }
       } else {
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt)
@@ -647,17 +650,18 @@ struct Plan {
 };
 
 int BitsOf(int fmt) { return fmt == kInt8 ? 8 : (fmt == kBf16 ? 16 : 4); }
-int ChunkRowStride(int fmt, int rt) { return kCopyBytes / rt + (BitsOf(fmt) == 4 ? 32 : 64); }
-int ChunkK(int fmt, int rt) { return kCopyBytes / rt * 8 / BitsOf(fmt); }
+int ChunkRowBytes(int mb, int rt) { return mb == 1 ? kCopyBytes : kCopyBytes / rt; }
+int ChunkRowStride(int fmt, int mb, int rt) { return ChunkRowBytes(mb, rt) + (BitsOf(fmt) == 4 ? 32 : 64); }
+int ChunkK(int fmt, int mb, int rt) { return ChunkRowBytes(mb, rt) * 8 / BitsOf(fmt); }
 
 size_t SmemFor(const Plan& pl, int M, int k_per_cta) {
   const int R = 16 * pl.rt, MP = 8 * pl.mb, groups = k_per_cta / kGroupK;
   size_t off = (static_cast<size_t>(2 * pl.stages) * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(2) * R * MP * 4 * ((pl.mb == 1 && pl.rt == 1) ? kConsumerWarps : 1);
+  off += static_cast<size_t>(2) * R * MP * 4 * (pl.mb == 1 ? kConsumerWarps : 1);
   off += (static_cast<size_t>(groups) * MP * 4 + 127) & ~static_cast<size_t>(127);
   off += (static_cast<size_t>(groups) * M * 128 + 127) & ~static_cast<size_t>(127);
   if (pl.grouped) off += (static_cast<size_t>(2) * groups * R * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(pl.stages) * R * ChunkRowStride(pl.fmt, pl.rt);
+  off += static_cast<size_t>(pl.stages) * R * ChunkRowStride(pl.fmt, pl.mb, pl.rt);
   return off;
 }
 
@@ -698,7 +702,7 @@ b200_status Validate(const b200_qmm_params* p) {
   return B200_OK;
 }
 
-b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan* out) {
+b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, Plan* out, bool no_tall_tiles) {
   Plan pl;
   pl.fmt = p->bits == 16 ? kBf16 : (p->bits == 8 ? kInt8 : (p->nibble_order ? kInt4Half : kInt4Seq));
   pl.grouped = (p->bits == 4) || (p->bits == 8 && p->group == 64);
@@ -707,6 +711,9 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   // x is staged once per (persistent) CTA, so the tile height only has to give
   // the x fragments some register reuse at larger batches.
   pl.rt = pl.mb;
+  // Up to 8 rows of x: two 16-row tiles per step (two independent dequant/MMA chains per
+  // warp) when 32-row tiles still give every SM one; only on the unrolled K = 4096 path.
+  if (pl.mb == 1 && K == 64 * kGroupK && CeilDiv(N, 32) >= sm_count && !no_tall_tiles) pl.rt = 2;
   pl.tiles = static_cast<int>(CeilDiv(N, 16 * pl.rt));
   // K is split across a cluster only when the row tiles alone cannot occupy the
   // GPU, or when a CTA's slice of x would not fit shared memory.
@@ -727,7 +734,7 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   if (!found)
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: M=%d K=%d does not fit the shared-memory staging of x", M, K);
   const int kc = K / pl.split;
-  const int chunks = static_cast<int>(CeilDiv(kc, ChunkK(pl.fmt, pl.rt)));
+  const int chunks = static_cast<int>(CeilDiv(kc, ChunkK(pl.fmt, pl.mb, pl.rt)));
   // One persistent CTA per SM (it walks tiles blockIdx.x, + grid, ...) with a deep
   // ring: under load a bulk copy takes ~3 us to land, so ~6.5 TB/s needs well
   // over 100 KB in flight per SM.
@@ -743,10 +750,16 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
     if (pl.smem <= budget || pl.stages <= min_stages) break;
     --pl.stages;
   }
-  if (pl.smem > static_cast<size_t>(max_smem))
+  if (pl.smem > static_cast<size_t>(max_smem)) {
+    if (pl.mb == 1 && pl.rt == 2 && !no_tall_tiles) return MakePlanImpl(p, sm_count, max_smem, out, true);
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: needs %zu bytes of shared memory (limit %d)", pl.smem, max_smem);
+  }
   *out = pl;
   return B200_OK;
+}
+
+b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan* out) {
+  return MakePlanImpl(p, sm_count, max_smem, out, false);
 }
 
 template <int FMT, int MB, int RT, bool GROUPED, int KG>
@@ -771,6 +784,7 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
       if (args.k_per_cta == 64 * kGroupK) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
+    case 12: return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
     case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
   }
