@@ -141,6 +141,54 @@ __device__ __forceinline__ void load_a(const uint8_t* row_group_ptr, int t, uint
   }
 }
 
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+
+// Same as load_a, from a 32-bit shared-memory address that already includes the thread's
+// offset (the unrolled path keeps these offsets in registers instead of re-deriving them).
+template <int FMT>
+__device__ __forceinline__ void load_a32(uint32_t addr, uint32_t (&a)[8]) {
+  if (FMT == kInt4Seq || FMT == kInt4Half) {
+    const uint2 w = lds64(addr);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      a[r] = lop3_and_or(r == 0 ? w.x : mulhi_shift(w.x, 1u << (32 - 4 * r)), 0x000f000fu, 0x43004300u);
+      a[4 + r] = lop3_and_or(r == 0 ? w.y : mulhi_shift(w.y, 1u << (32 - 4 * r)), 0x000f000fu, 0x43004300u);
+    }
+  } else if (FMT == kInt8) {
+    const uint4 w = lds128(addr);
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t u = words[j] ^ 0x80808080u;
+      const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+      const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+      const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+      const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+      a[2 * j] = pack_bf16(f0, f1);
+      a[2 * j + 1] = pack_bf16(f2, f3);
+    }
+  } else {
+    const uint4 w0 = lds128(addr);
+    const uint4 w1 = lds128(addr + 64);
+    a[0] = w0.x; a[1] = w0.y; a[2] = w0.z; a[3] = w0.w;
+    a[4] = w1.x; a[5] = w1.y; a[6] = w1.z; a[7] = w1.w;
+  }
+}
+
 __device__ __forceinline__ void consumer_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
@@ -504,13 +552,59 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       }
     };
 
+    // the same step from 32-bit shared addresses (thread offsets already added)
+    auto do_group32 = [&](uint32_t a_addr, uint32_t so_addr, const uint32_t (&xf)[MB][8], const float (&xs2)[MB][2]) {
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        uint32_t a0[8], a1[8];
+        load_a32<FMT>(a_addr + rt * 16 * kRowStride, a0);
+        load_a32<FMT>(a_addr + (rt * 16 + 8) * kRowStride, a1);
+        if (GROUPED) {
+          const float2 p0 = lds64f(so_addr + rt * 16 * 8), p1 = lds64f(so_addr + (rt * 16 + 8) * 8);
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb) {
+            float tmp[4];
+            mma_bf16_16816_z(tmp, a0[0], a1[0], a0[1], a1[1], xf[mb][0], xf[mb][1]);
+#pragma unroll
+            for (int i = 1; i < 4; ++i)
+              mma_bf16_16816(tmp, a0[2 * i], a1[2 * i], a0[2 * i + 1], a1[2 * i + 1], xf[mb][2 * i], xf[mb][2 * i + 1]);
+            if (F::kBits == 4) {
+              acc[rt][mb][0] = fmaf(p0.x, tmp[0], fmaf(p0.y, xs2[mb][0], acc[rt][mb][0]));
+              acc[rt][mb][1] = fmaf(p0.x, tmp[1], fmaf(p0.y, xs2[mb][1], acc[rt][mb][1]));
+              acc[rt][mb][2] = fmaf(p1.x, tmp[2], fmaf(p1.y, xs2[mb][0], acc[rt][mb][2]));
+              acc[rt][mb][3] = fmaf(p1.x, tmp[3], fmaf(p1.y, xs2[mb][1], acc[rt][mb][3]));
+            } else {
+              acc[rt][mb][0] = fmaf(p0.x, tmp[0], acc[rt][mb][0]);
+              acc[rt][mb][1] = fmaf(p0.x, tmp[1], acc[rt][mb][1]);
+              acc[rt][mb][2] = fmaf(p1.x, tmp[2], acc[rt][mb][2]);
+              acc[rt][mb][3] = fmaf(p1.x, tmp[3], acc[rt][mb][3]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              mma_bf16_16816(acc[rt][mb], a0[2 * i], a1[2 * i], a0[2 * i + 1], a1[2 * i + 1], xf[mb][2 * i],
+                             xf[mb][2 * i + 1]);
+        }
+      }
+    };
+
     constexpr int GC = kChunkK / kGroupK;                       // groups per chunk
     constexpr int GPW = KG > 0 ? KG / kConsumerWarps : 1;       // groups per warp (fast path)
     uint32_t xr[GPW][MB][8];
     float xq[GPW][MB][2];
+    uint32_t a_off[GPW], so_off[GPW];   // this thread's byte offsets inside a stage / a scale buffer
+    const uint32_t stage0 = smem_u32(stage_base), so0 = smem_u32(so);
     if (KG > 0) {
 #pragma unroll
-      for (int j = 0; j < GPW; ++j) load_x(warp + kConsumerWarps * j, xr[j], xq[j]);
+      for (int j = 0; j < GPW; ++j) {
+        load_x(warp + kConsumerWarps * j, xr[j], xq[j]);
+        const int gs = warp + (kConsumerWarps * j) % GC;
+        a_off[j] = static_cast<uint32_t>(gs * F::kGroupBytes + g * kRowStride + t * (F::kBits == 4 ? 8 : 16));
+        so_off[j] = static_cast<uint32_t>(((warp + kConsumerWarps * j) * R + g) * 8);
+      }
     }
 
     for (int ti = 0; ti < n_my; ++ti) {
@@ -537,10 +631,10 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
               dead = true;
             }
           }
-          const int gs = warp + (kConsumerWarps * j) % GC;
-          if (!dead)
-            do_group(stage_base + static_cast<size_t>(s) * kStageBytes + gs * F::kGroupBytes,
-                     so_cur + (warp + kConsumerWarps * j) * R, xr[j], xq[j]);
+          // (after a timed-out wait this multiplies stale shared memory; the result is discarded
+          // with the reported error, and skipping the branch keeps the loop straight-line)
+          do_group32(stage0 + static_cast<uint32_t>(s) * kStageBytes + a_off[j],
+                     so0 + static_cast<uint32_t>((ti & 1) * so_buf * 8) + so_off[j], xr[j], xq[j]);
           if (last) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
