@@ -8,8 +8,9 @@
 // steel_gemm.cc:115-138) with three B200 kernels:
 //   tcgen05  - TMA-fed tensor-core tiles with TMEM accumulators (gemm_tcgen05.cu),
 //              for 16-bit operands whose layout the TMA descriptors accept;
-//   few-row  - the bandwidth-bound streaming kernel (qmm.cu, 16-bit weights),
-//              for x . W^T with up to 32 rows on either side;
+//   few-row  - the bandwidth-bound streaming kernels: qmm.cu (16-bit weights) for
+//              x . W^T with up to 32 rows on either side, gemv_nn.cu for x . W with
+//              W stored [K][N] and up to 8 rows of x;
 //   SIMT     - the general tile kernel below: every dtype, transpose, stride,
 //              batch and beta; true f32 arithmetic for f32 operands (tensor
 //              cores have no f32 multiply, and the f32 block must hold rtol 1e-5).
@@ -22,6 +23,9 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
                         int64_t R, int64_t V, int64_t K, int64_t ld_vec, int64_t out_row_stride,
                         int64_t out_vec_stride, float alpha, int act, const void* bias, int bias_by_vec,
                         void* aux, int out_f32);
+// gemv_nn.cu
+bool FewRowNnSupports(const b200_gemm_params* p);
+b200_status RunFewRowNn(b200_context* ctx, cudaStream_t stream, const b200_gemm_params* p, const b200_epilogue* epi);
 // gemm_tcgen05.cu
 bool Tcgen05Supports(const b200_gemm_params* p, const b200_epilogue* epi);
 b200_status RunTcgen05(b200_context* ctx, cudaStream_t stream, const b200_gemm_params* p, const b200_epilogue* epi);
@@ -186,7 +190,7 @@ bool FewRowSupports(const b200_gemm_params* p, bool* vectors_are_b) {
 int Route(const b200_gemm_params* p, const b200_epilogue* epi, int forced) {
   if (p->m == 0 || p->n == 0 || p->batch == 0) return B200_ROUTE_NONE;
   if (forced == B200_ROUTE_SIMT) return B200_ROUTE_SIMT;
-  const bool few = FewRowSupports(p, nullptr);
+  const bool few = FewRowSupports(p, nullptr) || FewRowNnSupports(p);
   const bool tc = Tcgen05Supports(p, epi);
   if (forced == B200_ROUTE_FEWROW && few) return B200_ROUTE_FEWROW;
   if (forced == B200_ROUTE_TCGEN05 && tc) return B200_ROUTE_TCGEN05;
@@ -225,6 +229,7 @@ b200_status b200_gemm(b200_context* ctx, b200_stream stream, const b200_gemm_par
   const int route = Route(p, epi, ctx->force_route.load());
   if (route == B200_ROUTE_NONE) return B200_OK;
   if (route == B200_ROUTE_TCGEN05) return RunTcgen05(ctx, stream, p, epi);
+  if (route == B200_ROUTE_FEWROW && !FewRowSupports(p, nullptr)) return RunFewRowNn(ctx, stream, p, epi);
   if (route == B200_ROUTE_FEWROW) {
     bool vb = false;
     FewRowSupports(p, &vb);

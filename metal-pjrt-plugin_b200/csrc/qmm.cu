@@ -24,7 +24,10 @@
 //     across CTAs through a thread-block cluster's distributed shared memory.
 #include <cooperative_groups.h>
 
+#include <algorithm>
 #include <cstdlib>
+#include <map>
+#include <utility>
 
 #include "common.cuh"
 
@@ -228,15 +231,17 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
 // FMT: storage format; MB: batch blocks of 8; RT: 16-row tiles per CTA tile;
 // GROUPED: a scale (and offset) per 64 inputs, else one scale per row applied at the end.
 //
-// grid = (CTAs, split).  With split == 1 a CTA is persistent: it walks row tiles
-// blockIdx.x, blockIdx.x + gridDim.x, ... and stages x (and fused transforms)
-// once.  With split > 1 the grid has one CTA per (tile, K slice) and the slices
-// of a tile form a cluster that reduces through distributed shared memory.
+// grid = (CTAs or clusters, split).  CTAs are persistent: a CTA walks row tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... and stages its slice of x (and fused
+// transforms) once.  With split > 1 the `split` CTAs of a cluster take the K
+// slices of the same tiles; after every tile they meet on an mbarrier in each
+// other's shared memory and each finishes a share of the rows from all the
+// slices' partial tiles, read through distributed shared memory.
 // KG > 0: the CTA's K slice is exactly KG groups (and MB == 1): every warp owns
 // a compile-time set of KG / 16 groups, keeps their x fragments in registers for
 // all row tiles, and its loop over them is fully unrolled.  KG == 0: any K.
 template <int FMT, int MB, int RT, bool GROUPED, int KG>
-__global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   using F = Fmt<FMT>;
   constexpr int R = 16 * RT;
   constexpr int MP = 8 * MB;
@@ -251,8 +256,8 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int split = gridDim.y;
-  const bool persistent = split == 1;
+  const int split = gridDim.y;   // CTAs of one cluster along K; every CTA walks tiles blockIdx.x, + gridDim.x, ...
+  const bool solo = split == 1;
   const int k_begin = blockIdx.y * a.k_per_cta;
   const int groups_cta = a.k_per_cta / kGroupK;
   const int n_chunks = (a.k_per_cta + kChunkK - 1) / kChunkK;
@@ -265,11 +270,12 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + NS;
   size_t off = (static_cast<size_t>(2 * NS) * 8 + 127) & ~static_cast<size_t>(127);
-  // Cross-warp reduction buffer.  Small tiles (one MMA row tile, batch <= 8) in a
-  // persistent CTA: every warp stores its partial tile, [2][warps][R][MP], and the
-  // epilogue threads add the 16 partials.  Otherwise: [2][R][MP] added into atomically.
+  // Cross-warp reduction buffer.  Small tiles (one MMA row tile, batch <= 8) without a
+  // split of K: every warp stores its partial tile, [2][warps][R][MP], and the
+  // epilogue threads add the 16 partials.  Otherwise: [2][R][MP] added into atomically
+  // (with K split across a cluster, the tile the peers read through distributed shared memory).
   constexpr bool kPartials = MB == 1;
-  const bool partials = kPartials && persistent;
+  const bool partials = kPartials && solo;
   float* red = reinterpret_cast<float*>(smem + off);
   off += static_cast<size_t>(2) * R * MP * 4 * (kPartials ? kConsumerWarps : 1);
   float* xsum = reinterpret_cast<float*>(smem + off);                // [groups_cta][MP]
@@ -282,18 +288,22 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
   uint8_t* stage_base = smem + off;
   __shared__ float ss_part[kConsumerWarps][8];
   __shared__ float rinv[8];
+  __shared__ __align__(8) uint64_t tile_bar[2];   // K split: "every CTA of the cluster has finished tile ti"
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kConsumerWarps);
     }
+    mbar_init(&tile_bar[0], split);
+    mbar_init(&tile_bar[1], split);
     mbar_fence_init();
   }
   if (!partials)
     for (int i = tid; i < 2 * R * MP; i += kThreads) red[i] = 0.0f;
   for (int i = tid; i < groups_cta * MP; i += kThreads) xsum[i] = 0.0f;
   __syncthreads();
+  if (!solo) cg::this_cluster().sync();   // the peers' barriers exist before anyone arrives on them
 
   bool dead = false;  // a bounded wait gave up: skip the work, keep every barrier
 
@@ -481,9 +491,16 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
     }
     consumer_barrier();
 
-    float acc[RT][MB][4];
+    // Batches above 8 (MB > 1): the 16 warps split the tile's RT row tiles as well as K
+    // (warp w takes row tile w % RT and every (16 / RT)-th group), so a warp keeps one row
+    // tile of accumulators and adds it into the shared tile once per 16 / RT groups' worth
+    // of work.  Up to 8: every warp covers all RT row tiles of its groups.
+    constexpr int kRowSplit = MB > 1 ? RT : 1;    // warps along the rows of a tile
+    constexpr int RTW = RT / kRowSplit;           // row tiles per warp
+    const int row_base = (warp % kRowSplit) * 16;
+    float acc[RTW][MB][4];
 #pragma unroll
-    for (int rt = 0; rt < RT; ++rt)
+    for (int rt = 0; rt < RTW; ++rt)
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
@@ -515,8 +532,8 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
     auto do_group = [&](const uint8_t* stage_group, const float2* so_group, const uint32_t (&xf)[MB][8],
                         const float (&xs2)[MB][2]) {
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-        const int r0 = rt * 16 + g, r1 = r0 + 8;
+      for (int rt = 0; rt < RTW; ++rt) {
+        const int r0 = row_base + rt * 16 + g, r1 = r0 + 8;
         uint32_t a0[8], a1[8];
         load_a<FMT>(stage_group + r0 * kRowStride, t, a0);
         load_a<FMT>(stage_group + r1 * kRowStride, t, a1);
@@ -555,7 +572,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
     // the same step from 32-bit shared addresses (thread offsets already added)
     auto do_group32 = [&](uint32_t a_addr, uint32_t so_addr, const uint32_t (&xf)[MB][8], const float (&xs2)[MB][2]) {
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
+      for (int rt = 0; rt < RTW; ++rt) {
         uint32_t a0[8], a1[8];
         load_a32<FMT>(a_addr + rt * 16 * kRowStride, a0);
         load_a32<FMT>(a_addr + (rt * 16 + 8) * kRowStride, a1);
@@ -607,6 +624,18 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
       }
     }
 
+    // Consumer threads only.  Caller has passed consumer_barrier(), so the CTA's adds into
+    // the tile's buffer are ordered before thread 0's release-arrivals.
+    auto cluster_tile_barrier = [&](int ti) {
+      uint64_t* bar = &tile_bar[ti & 1];
+      if (tid == 0)
+        for (int c = 0; c < split; ++c) mbar_arrive_cluster(bar, static_cast<uint32_t>(c));
+      if (!dead && !mbar_wait_bounded_cluster(bar, static_cast<uint32_t>(ti >> 1) & 1u)) {
+        report_timeout(a.status, 300 + (ti & 1));
+        dead = true;
+      }
+    };
+
     for (int ti = 0; ti < n_my; ++ti) {
       const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
       const int rows_valid = min(R, a.N - n0);
@@ -649,7 +678,7 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
             dead = true;
           }
           const int chunk_groups = min(kChunkK, a.k_per_cta - c * kChunkK) / kGroupK;
-          for (int gs = warp; gs < chunk_groups && !dead; gs += kConsumerWarps) {
+          for (int gs = warp / kRowSplit; gs < chunk_groups && !dead; gs += kConsumerWarps / kRowSplit) {
             const int gl = c * GC + gs;     // group within this CTA's slice
             uint32_t xf[MB][8];
             float xs2[MB][2];
@@ -665,27 +694,27 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
         // plain stores of this warp's partial tile: lane (g, t) holds rows g, g+8, columns 2t, 2t+1
         float* mine = red_cur + warp * R * MP;
 #pragma unroll
-        for (int rt = 0; rt < RT; ++rt) {
+        for (int rt = 0; rt < RTW; ++rt) {
           *reinterpret_cast<float2*>(&mine[(rt * 16 + g) * MP + 2 * t]) = make_float2(acc[rt][0][0], acc[rt][0][1]);
           *reinterpret_cast<float2*>(&mine[(rt * 16 + g + 8) * MP + 2 * t]) = make_float2(acc[rt][0][2], acc[rt][0][3]);
           acc[rt][0][0] = acc[rt][0][1] = acc[rt][0][2] = acc[rt][0][3] = 0.0f;
         }
       } else {
 #pragma unroll
-        for (int rt = 0; rt < RT; ++rt)
+        for (int rt = 0; rt < RTW; ++rt)
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const int row = rt * 16 + g + ((i & 2) ? 8 : 0);
+              const int row = row_base + rt * 16 + g + ((i & 2) ? 8 : 0);
               const int col = mb * 8 + 2 * t + (i & 1);
               atomicAdd(&red_cur[row * MP + col], acc[rt][mb][i]);
               acc[rt][mb][i] = 0.0f;
             }
       }
       if (has_next) scale_store(n0 + static_cast<int>(gridDim.x) * R, so + ((ti + 1) & 1) * so_buf);
-      if (persistent) {
-        consumer_barrier();
+      consumer_barrier();
+      if (solo) {
         if (partials) {
           // the epilogue moves to other warps every tile, so no warp is always the late one
           const int et = (tid + kConsumerThreads - ((ti * 128) % kConsumerThreads)) % kConsumerThreads;
@@ -704,33 +733,34 @@ __global__ void __launch_bounds__(kThreads) qgemv_kernel(const QmmArgs a) {
             store_output<FMT, GROUPED>(a, v, m, n0 + r);
           }
         }
+      } else {
+        // K split across the cluster: tell every CTA this one's tile is complete, wait for
+        // all of theirs, then finish this CTA's share of the rows from the peers' tiles.
+        cluster_tile_barrier(ti);
+        const int rows_per_rank = (R + split - 1) / split;
+        const int r_begin = static_cast<int>(blockIdx.y) * rows_per_rank;
+        const int r_count = min(min(r_begin + rows_per_rank, R), rows_valid) - r_begin;
+        if (r_count > 0 && !dead) {
+          cg::cluster_group cluster = cg::this_cluster();
+          for (int idx = tid; idx < r_count * a.M; idx += kConsumerThreads) {
+            const int r = r_begin + idx % r_count, m = idx / r_count;
+            float v = 0.0f;
+            for (int c = 0; c < split; ++c) v += cluster.map_shared_rank(red_cur, c)[r * MP + m];
+            store_output<FMT, GROUPED>(a, v, m, n0 + r);
+          }
+        }
+        // The peers finished reading the previous tile's buffer before they arrived for
+        // this one: clear it for the tile after this.
+        if (ti > 0) {
+          float* prev = red + ((ti + 1) & 1) * R * MP;
+          for (int i = tid; i < R * MP; i += kConsumerThreads) prev[i] = 0.0f;
+        }
+        consumer_barrier();
       }
     }
+    // no CTA leaves while a peer may still read its last tile
+    if (!solo) cluster_tile_barrier(n_my);
   }
-  if (persistent) return;
-
-  // ---- split-K across the cluster (one tile per CTA), then the epilogue -----------------
-  __syncthreads();
-  cg::cluster_group cluster = cg::this_cluster();
-  cluster.sync();
-  {
-    const int n0 = static_cast<int>(blockIdx.x) * R;
-    const int rows_valid = min(R, a.N - n0);
-    const int rows_per_rank = (R + split - 1) / split;
-    const int r_begin = blockIdx.y * rows_per_rank;
-    const int r_end = min(min(r_begin + rows_per_rank, R), rows_valid);
-    const int r_count = r_end - r_begin;
-    if (r_count > 0) {
-      for (int idx = tid; idx < r_count * a.M; idx += kThreads) {
-        const int r = r_begin + idx % r_count;
-        const int m = idx / r_count;
-        float v = 0.0f;
-        for (int c = 0; c < split; ++c) v += cluster.map_shared_rank(red, c)[r * MP + m];
-        store_output<FMT, GROUPED>(a, v, m, n0 + r);
-      }
-    }
-  }
-  cluster.sync();  // peers may still be reading this CTA's tile
 }
 
 // ---------------------------------------------------------------------------
@@ -802,8 +832,8 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
   pl.grouped = (p->bits == 4) || (p->bits == 8 && p->group == 64);
   const int M = static_cast<int>(p->M), N = static_cast<int>(p->N), K = static_cast<int>(p->K);
   pl.mb = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-  // x is staged once per (persistent) CTA, so the tile height only has to give
-  // the x fragments some register reuse at larger batches.
+  // Above 8 batch rows the tile grows with the batch: its row tiles are shared out among
+  // the warps, so each warp reduces into the shared tile less often.
   pl.rt = pl.mb;
   // Up to 8 rows of x: two 16-row tiles per step (two independent dequant/MMA chains per
   // warp) when 32-row tiles still give every SM one; only on the unrolled K = 4096 path.
@@ -811,42 +841,35 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
   pl.tiles = static_cast<int>(CeilDiv(N, 16 * pl.rt));
   // K is split across a cluster only when the row tiles alone cannot occupy the
   // GPU, or when a CTA's slice of x would not fit shared memory.
-  const size_t x_budget = 96 * 1024;
-  bool found = false;
-  for (int split = 1; split <= 8; split <<= 1) {
-    if (K % (split * kGroupK) != 0) break;
-    const int kc = K / split;
-    if (static_cast<size_t>(M) * kc * 2 > x_budget) continue;
-    const bool fills = static_cast<int64_t>(pl.tiles) * split >= sm_count;
-    const bool last = split == 8 || K % (2 * split * kGroupK) != 0;
-    if (fills || last) {
-      pl.split = split;
-      found = true;
-      break;
-    }
-  }
-  if (!found)
-    return Fail(B200_UNIMPLEMENTED, "b200_qmm: M=%d K=%d does not fit the shared-memory staging of x", M, K);
-  const int kc = K / pl.split;
-  const int chunks = static_cast<int>(CeilDiv(kc, ChunkK(pl.fmt, pl.mb, pl.rt)));
   // One persistent CTA per SM (it walks tiles blockIdx.x, + grid, ...) with a deep
   // ring: under load a bulk copy takes ~3 us to land, so ~6.5 TB/s needs well
-  // over 100 KB in flight per SM.
-  const int ctas_per_sm = 1;
-  pl.grid_x = pl.split > 1 ? pl.tiles : std::min(pl.tiles, sm_count * ctas_per_sm);
-  const int units = chunks * static_cast<int>(CeilDiv(pl.tiles, pl.grid_x));
-  // Ring depth: as many stages as the CTA has units, within ~200 KB.
-  const size_t budget = 200 * 1024;
-  pl.stages = std::min(units, 12);
-  const int min_stages = units < 2 ? 1 : 2;
-  for (;;) {
-    pl.smem = SmemFor(pl, M, kc);
-    if (pl.smem <= budget || pl.stages <= min_stages) break;
-    --pl.stages;
+  // over 100 KB in flight per SM.  Ring depth: as many stages as the CTA has units,
+  // within ~200 KB.
+  const size_t x_budget = 96 * 1024, budget = 200 * 1024;
+  bool found = false;
+  for (int split = 1; split <= 8 && !found; split <<= 1) {
+    if (K % (split * kGroupK) != 0) break;
+    const int kc = K / split;
+    const bool fills = static_cast<int64_t>(pl.tiles) * split >= sm_count;
+    const bool last = split == 8 || K % (2 * split * kGroupK) != 0;
+    if (static_cast<size_t>(M) * kc * 2 > x_budget || !(fills || last)) continue;
+    pl.split = split;
+    const int chunks = static_cast<int>(CeilDiv(kc, ChunkK(pl.fmt, pl.mb, pl.rt)));
+    pl.grid_x = std::min(pl.tiles, std::max(1, sm_count / split));
+    const int units = chunks * static_cast<int>(CeilDiv(pl.tiles, pl.grid_x));
+    pl.stages = std::min(units, 12);
+    const int min_stages = units < 2 ? 1 : 2;
+    for (;;) {
+      pl.smem = SmemFor(pl, M, kc);
+      if (pl.smem <= budget || pl.stages <= min_stages) break;
+      --pl.stages;
+    }
+    found = pl.smem <= static_cast<size_t>(max_smem);   // else: a smaller slice of K per CTA
+    if (pl.rt > pl.mb) break;   // the two-tile variant exists for the whole K = 4096 only
   }
-  if (pl.smem > static_cast<size_t>(max_smem)) {
+  if (!found) {
     if (pl.mb == 1 && pl.rt == 2 && !no_tall_tiles) return MakePlanImpl(p, sm_count, max_smem, out, true);
-    return Fail(B200_UNIMPLEMENTED, "b200_qmm: needs %zu bytes of shared memory (limit %d)", pl.smem, max_smem);
+    return Fail(B200_UNIMPLEMENTED, "b200_qmm: M=%d K=%d does not fit shared memory (limit %d bytes)", M, K, max_smem);
   }
   *out = pl;
   return B200_OK;
@@ -868,6 +891,32 @@ cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
   lc.stream = stream;
   lc.pdl = true;
   lc.cluster_y = pl.split;
+  if (pl.split > 1) {
+    // Persistent clusters: no more of them than the GPU holds at once (a GPC takes only
+    // whole clusters), or the surplus would run alone after the others finish.
+    static std::mutex mu;
+    static std::map<std::pair<int, size_t>, int> resident;   // (split, smem) -> clusters
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = resident.find({pl.split, pl.smem});
+    if (it == resident.end()) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(64, pl.split, 1);
+      cfg.blockDim = lc.block;
+      cfg.dynamicSmemBytes = pl.smem;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 1;
+      attr.val.clusterDim.y = pl.split;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+      if (e != cudaSuccess) return e;
+      it = resident.emplace(std::make_pair(pl.split, pl.smem), std::max(n, 1)).first;
+    }
+    lc.grid.x = std::min<unsigned>(lc.grid.x, static_cast<unsigned>(it->second));
+  }
   return Launch(lc, kernel, args);
 }
 
@@ -878,7 +927,9 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
       if (args.k_per_cta == 64 * kGroupK) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
-    case 12: return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
+    case 12:
+      if (args.k_per_cta != 64 * kGroupK) return cudaErrorInvalidValue;
+      return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
     case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
   }

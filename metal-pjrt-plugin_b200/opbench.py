@@ -155,7 +155,8 @@ def main():
     if a.op == "qmm":
         print(json.dumps(bench_qmm(pkg, a.bits, a.m, a.n, a.k, a.buffers, a.reps, a.group)), flush=True)
     elif a.op == "gemm":
-        print(json.dumps(bench_gemm(pkg, a.m, a.n, a.k, a.act, a.bias, a.reps, a.dtype, a.tb, min(a.buffers, 4))), flush=True)
+        print(json.dumps(bench_gemm(pkg, a.m, a.n, a.k, a.act, a.bias, a.reps, a.dtype, a.tb,
+                                    max(4, min(a.buffers, int(512e6 // (a.n * a.k * 2)))))), flush=True)
     elif a.op == "rows":
         print(json.dumps(bench_rows(pkg, a.kind, a.rows, a.n, a.dtype, a.reps)), flush=True)
     else:

@@ -87,7 +87,12 @@ def test_gemm_route_table():
     assert route(_gemm(p, 33, 4096, 1024, tb=1)) != L.ROUTE_FEWROW
     assert route(_gemm(p, 4, 4096, 448, tb=1)) != L.ROUTE_FEWROW                     # K below 512
     assert route(_gemm(p, 4, 4096, 1000, tb=1)) != L.ROUTE_FEWROW                    # K not a multiple of 64
-    assert route(_gemm(p, 4, 4096, 1024, tb=0)) != L.ROUTE_FEWROW                    # NN layout
+    for m in (1, 2, 8):
+        assert route(_gemm(p, m, 4096, 1024, tb=0)) == L.ROUTE_FEWROW                # x . W with W stored [K][N]
+    assert route(_gemm(p, 4, 4096, 1024, tb=0, dtype=L.F16)) == L.ROUTE_FEWROW
+    assert route(_gemm(p, 9, 4096, 1024, tb=0)) != L.ROUTE_FEWROW
+    assert route(_gemm(p, 4, 4100, 1024, tb=0)) != L.ROUTE_FEWROW                    # N not a multiple of 8
+    assert route(_gemm(p, 4, 4096, 1024, tb=0, beta=1.0)) != L.ROUTE_FEWROW
     assert route(_gemm(p, 4, 4096, 1024, tb=1, dtype=L.F16)) != L.ROUTE_FEWROW
     assert route(_gemm(p, 4, 4096, 1024, tb=1, beta=1.0)) != L.ROUTE_FEWROW
     assert route(_gemm(p, 4, 4096, 1024, tb=1, batch=2)) != L.ROUTE_FEWROW
@@ -133,6 +138,11 @@ def test_qmm_validate_and_plan():
     assert plan(16, 4096, 4096)[0] == 32 and plan(16, 4096, 4096)[2] == 2
     r32, s32, mb32 = plan(32, 4096, 12288)
     assert mb32 == 4 and 32 * (12288 // s32) * 2 <= 96 * 1024
+    # every batch size up to 32 has a plan for the decoder's projection shapes, in all three formats
+    for n, k in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096)):
+        for m in range(1, 33):
+            for bits, group in ((4, 64), (8, 64), (8, k), (16, 0)):
+                assert plan(m, n, k, bits=bits, group=group)[0] in (16, 32, 64)
 
 
 def test_no_device_means_a_loud_failure():

@@ -119,6 +119,20 @@ def test_few_row_route(vecs, vectors_are_b):
     assert B_.gemm_route(prm) == p._lib.ROUTE_FEWROW
 
 
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("dt_in,dt_out", [("bf16", "bf16"), ("f16", "f16"), ("bf16", "f32")])
+def test_few_row_nn_route(m, dt_in, dt_out):
+    """x . W with W stored [K][N]: the streaming kernel for the NN layout, every row
+    count class, ragged N and K, padded rows, all epilogue parts."""
+    p = pkg()
+    for n, k in ((520, 1024), (264, 777), (4096, 512)):
+        run_case(m, n, k, dt_in=dt_in, dt_out=dt_out, pad=8, bias=True, act=3, aux=True, alpha=0.5, seed=m)
+    B_ = p.blas
+    A, Bm, D = dev(np.zeros((m, 1024), bf16)), dev(np.zeros((1024, 520), bf16)), dev(np.zeros((m, 520), bf16))
+    prm = B_.GemmParams(m, 520, 1024, B_.Operand(A, 1024), B_.Operand(Bm, 520), B_.Operand(D, 520))
+    assert B_.gemm_route(prm) == p._lib.ROUTE_FEWROW
+
+
 def test_config1_f32_block():
     """x[512,1024] @ W[1024,1024] + b, then RMSNorm: f32, rtol 1e-5."""
     p = pkg()

@@ -80,7 +80,7 @@ def test_int4_product(m, k, n):
 
 
 @pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (8, 4096, 12288), (32, 12288, 4096), (1, 12288, 4096),
-                                   (32, 4096, 1024)])
+                                   (32, 4096, 1024), (4, 12288, 4096), (5, 12288, 512), (16, 12288, 4096)])
 def test_int4_product_qwen3_shapes(m, k, n):
     """Full Qwen3-8B projection shapes.  The CPU side checks a sample of the
     outputs (512 columns) so the suite stays fast."""
