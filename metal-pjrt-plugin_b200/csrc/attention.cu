@@ -86,12 +86,14 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
   __shared__ float red[G][kThreads / 32];
   __shared__ float knew[2][HALF + 4];
   __shared__ float vnew[D];
-  pdl_wait();
+  // The position and the cache slots of earlier steps do not come from the kernel before
+  // this one, so they are requested before waiting for it.
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z;
   const int pos = *a.pos;
   if (pos < 0 || pos >= a.max_len) {         // nothing may be written outside the cache
+    pdl_wait();
     if (tid == 0 && a.status != nullptr) atomicCAS(a.status, 0, static_cast<int>(B200_INVALID_ARGUMENT));
     return;
   }
@@ -99,7 +101,10 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
   const int n_valid = pos + 1;
   const int n_old = fused ? pos : pos + 1;   // slots whose K/V are already in the cache
   const int s0 = split * kChunk;
-  if (s0 >= n_valid) return;                 // the merge only reads splits below n_valid
+  if (s0 >= n_valid) {                       // the merge only reads splits below n_valid
+    pdl_wait();
+    return;
+  }
   const int cnt = min(kChunk, n_valid - s0);
   const bool owner = fused && pos >= s0 && pos < s0 + kChunk;
   const int64_t bkv = static_cast<int64_t>(b) * a.kv_heads + kv;
@@ -122,6 +127,7 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
   }
 
   // ---- queries (and, in the owning CTA, the new key and value) -----------------------
+  pdl_wait();   // q (or the fused qkv row) is the previous kernel's output
   if (fused) {
     const int total_heads = a.heads + 2 * a.kv_heads;
     const __nv_bfloat16* row = a.qkv + static_cast<int64_t>(b) * total_heads * D;
