@@ -241,11 +241,17 @@ def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
     for x, w in jobs[:8]:
         pkg.qwen3.linear(x, w, ctx=ctx)
     torch.cuda.synchronize()
+    # one CUDA graph of all the launches, so the figure is device time and not the host's launch rate
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for x, w in jobs:
+            pkg.qwen3.linear(x, w, ctx=ctx)
+    graph.replay()
+    torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(reps):
-        for x, w in jobs:
-            pkg.qwen3.linear(x, w, ctx=ctx)
+        graph.replay()
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop)

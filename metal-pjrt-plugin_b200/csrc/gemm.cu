@@ -8,12 +8,14 @@
 // steel_gemm.cc:115-138) with three B200 kernels:
 //   tcgen05  - TMA-fed tensor-core tiles with TMEM accumulators (gemm_tcgen05.cu),
 //              for 16-bit operands whose layout the TMA descriptors accept;
-//   few-row  - the bandwidth-bound streaming kernels: qmm.cu (16-bit weights) for
-//              x . W^T with up to 32 rows on either side, gemv_nn.cu for x . W with
-//              W stored [K][N] and up to 8 rows of x;
+//   few-row  - the bandwidth-bound streaming kernel (qmm.cu, 16-bit weights), for
+//              x . W^T with up to 32 rows on either side; preferred up to 8 rows, above
+//              that the tensor-core route (which splits K across a cluster) is faster;
 //   SIMT     - the general tile kernel below: every dtype, transpose, stride,
 //              batch and beta; true f32 arithmetic for f32 operands (tensor
 //              cores have no f32 multiply, and the f32 block must hold rtol 1e-5).
+#include <algorithm>
+
 #include "common.cuh"
 
 using namespace b200;
@@ -23,9 +25,6 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
                         int64_t R, int64_t V, int64_t K, int64_t ld_vec, int64_t out_row_stride,
                         int64_t out_vec_stride, float alpha, int act, const void* bias, int bias_by_vec,
                         void* aux, int out_f32);
-// gemv_nn.cu
-bool FewRowNnSupports(const b200_gemm_params* p);
-b200_status RunFewRowNn(b200_context* ctx, cudaStream_t stream, const b200_gemm_params* p, const b200_epilogue* epi);
 // gemm_tcgen05.cu
 bool Tcgen05Supports(const b200_gemm_params* p, const b200_epilogue* epi);
 b200_status RunTcgen05(b200_context* ctx, cudaStream_t stream, const b200_gemm_params* p, const b200_epilogue* epi);
@@ -190,11 +189,12 @@ bool FewRowSupports(const b200_gemm_params* p, bool* vectors_are_b) {
 int Route(const b200_gemm_params* p, const b200_epilogue* epi, int forced) {
   if (p->m == 0 || p->n == 0 || p->batch == 0) return B200_ROUTE_NONE;
   if (forced == B200_ROUTE_SIMT) return B200_ROUTE_SIMT;
-  const bool few = FewRowSupports(p, nullptr) || FewRowNnSupports(p);
+  const bool few = FewRowSupports(p, nullptr);
   const bool tc = Tcgen05Supports(p, epi);
   if (forced == B200_ROUTE_FEWROW && few) return B200_ROUTE_FEWROW;
   if (forced == B200_ROUTE_TCGEN05 && tc) return B200_ROUTE_TCGEN05;
-  if (few) return B200_ROUTE_FEWROW;
+  // measured on 4096 x 4096 weights: 9 vs 13 us at 1 row, 12 vs 14 at 8, 20 vs 13 at 16, 33 vs 16 at 32
+  if (few && (std::min(p->m, p->n) <= 8 || !tc)) return B200_ROUTE_FEWROW;
   if (tc) return B200_ROUTE_TCGEN05;
   return B200_ROUTE_SIMT;
 }
@@ -229,7 +229,6 @@ b200_status b200_gemm(b200_context* ctx, b200_stream stream, const b200_gemm_par
   const int route = Route(p, epi, ctx->force_route.load());
   if (route == B200_ROUTE_NONE) return B200_OK;
   if (route == B200_ROUTE_TCGEN05) return RunTcgen05(ctx, stream, p, epi);
-  if (route == B200_ROUTE_FEWROW && !FewRowSupports(p, nullptr)) return RunFewRowNn(ctx, stream, p, epi);
   if (route == B200_ROUTE_FEWROW) {
     bool vb = false;
     FewRowSupports(p, &vb);

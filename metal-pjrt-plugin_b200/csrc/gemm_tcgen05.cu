@@ -19,10 +19,14 @@
 // Either operand may be transposed: a K-contiguous operand is loaded as [rows][64 k] boxes
 // (K-major descriptor), an M- or N-contiguous one as [64 k][64 rows] boxes (MN-major
 // descriptor), so nothing is transposed in memory.
+#include <cooperative_groups.h>
 #include <cuda.h>
+
+#include <mutex>
 
 #include "common.cuh"
 
+namespace cg = cooperative_groups;
 using namespace b200;
 
 namespace {
@@ -43,6 +47,7 @@ struct TcArgs {
   int out_dtype;   // b200_dtype of D
   int ta, tb;
   int tiles_m, tiles_n;
+  int split;       // CTAs of a cluster along K (grid.y); 1: persistent CTAs, no cluster
   int* status;
 };
 
@@ -168,6 +173,47 @@ __device__ __forceinline__ void epilogue_row(const TcArgs& a, const uint32_t (&v
   }
 }
 
+// The same epilogue for 4 consecutive columns (the split-K reduction, where a warp owns a
+// row and its lanes adjacent float4s, so that the reads of the peers' tiles coalesce).
+template <typename TOut>
+__device__ __forceinline__ void epilogue_quad(const TcArgs& a, const float (&acc)[4], int row, int col0) {
+  TOut* D = static_cast<TOut*>(a.d);
+  TOut* AUX = static_cast<TOut*>(a.aux);
+  const TOut* bias = static_cast<const TOut*>(a.bias);
+  const int64_t o = static_cast<int64_t>(row) * a.ldd + col0;
+  float x[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    x[j] = a.alpha * acc[j];
+    if (col0 + j < a.n) {
+      if (a.beta != 0.0f) x[j] += a.beta * load_as_f32<TOut>(D + o + j);
+      if (bias != nullptr) x[j] += load_as_f32<TOut>(bias + col0 + j);
+    }
+  }
+  constexpr size_t kBytes = 4 * sizeof(TOut);
+  const bool vec = col0 + 4 <= a.n && (a.ldd % 4 == 0) && (reinterpret_cast<uintptr_t>(D) % kBytes == 0) &&
+                   (AUX == nullptr || reinterpret_cast<uintptr_t>(AUX) % kBytes == 0);
+  if (vec) {
+    struct alignas(kBytes) Pack { TOut e[4]; };
+    Pack pd, pa;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      pa.e[j] = store_from_f32<TOut>(x[j]);
+      pd.e[j] = store_from_f32<TOut>(apply_act(a.act, x[j]));
+    }
+    if (AUX != nullptr) *reinterpret_cast<Pack*>(AUX + o) = pa;
+    *reinterpret_cast<Pack*>(D + o) = pd;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col0 + j < a.n) {
+        if (AUX != nullptr) AUX[o + j] = store_from_f32<TOut>(x[j]);
+        D[o + j] = store_from_f32<TOut>(apply_act(a.act, x[j]));
+      }
+    }
+  }
+}
+
 template <int BN, typename TOut>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a,
@@ -185,6 +231,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int num_tiles = a.tiles_m * a.tiles_n;
   const int k_iters = (a.k + BK - 1) / BK;
+  // With K split across a cluster, grid.x is the tile count (one tile per CTA) and CTA
+  // blockIdx.y accumulates k steps [ki_begin, ki_end) of it.
+  const int ki_begin = a.split > 1 ? static_cast<int>(blockIdx.y) * k_iters / a.split : 0;
+  const int ki_end = a.split > 1 ? (static_cast<int>(blockIdx.y) + 1) * k_iters / a.split : k_iters;
+  constexpr int kPartLd = BN + 4;          // row pitch (floats) of the partial tile in shared memory
   constexpr uint32_t kTmemCols = 2 * BN;   // two accumulators; a power of two >= 32
 
   if (tid == 0) {
@@ -213,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int tm = tile % a.tiles_m, tn = tile / a.tiles_m;
-        for (int ki = 0; ki < k_iters && ok; ++ki, ++it) {
+        for (int ki = ki_begin; ki < ki_end && ok; ++ki, ++it) {
           const int s = it % kStages, use = it / kStages;
           if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
             report_timeout(a.status, 300 + s);
@@ -254,7 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int ki = 0; ki < k_iters && ok; ++ki, ++it) {
+        for (int ki = ki_begin; ki < ki_end && ok; ++ki, ++it) {
           const int s = it % kStages;
           if (!mbar_wait_bounded(&full[s], (it / kStages) & 1)) {
             report_timeout(a.status, 320 + s);
@@ -268,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t da = a.ta ? make_desc(a_addr + kk * 2048, 8192, 1024) : make_desc(a_addr + kk * 32, 16, 1024);
             const uint64_t db = a.tb ? make_desc(b_addr + kk * 32, 16, 1024) : make_desc(b_addr + kk * 2048, 8192, 1024);
-            umma_f16(tmem_d, da, db, idesc, (ki > 0 || kk > 0) ? 1u : 0u);
+            umma_f16(tmem_d, da, db, idesc, (ki > ki_begin || kk > 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);     // the slot is free once these MMAs have read it
         }
@@ -295,12 +346,59 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(32 * q) << 16) + static_cast<uint32_t>(acc * BN + c0), v);
         const int col0 = tn * BN + c0;
-        if (row < a.m && col0 < a.n) epilogue_row<TOut>(a, v, row, col0);
+        if (a.split > 1) {
+          // this CTA's K slice only: park the f32 partial in the (now idle) ring
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(smem) + (32 * q + lane) * kPartLd + c0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                 __uint_as_float(v[4 * j + 3]));
+        } else if (row < a.m && col0 < a.n) {
+          epilogue_row<TOut>(a, v, row, col0);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+  }
+  if (a.split > 1) {
+    // K split: every CTA of the cluster finishes rows [rank, rank + 1) * 128 / split of the
+    // tile from all the partial tiles, read through distributed shared memory.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (warp >= 2) {
+      const int tile = blockIdx.x, tm = tile % a.tiles_m, tn = tile / a.tiles_m;
+      const int rows_per_rank = BM / a.split;
+      const float* part = reinterpret_cast<const float*>(smem);
+      // a warp per row, lanes on adjacent float4s: 512-byte runs of every peer's tile
+      for (int rr = warp - 2; rr < rows_per_rank; rr += kEpilogueWarps) {
+        const int r = static_cast<int>(blockIdx.y) * rows_per_rank + rr;
+        const int row = tm * BM + r;
+        if (row >= a.m) break;
+#pragma unroll
+        for (int t = 0; t < BN / 128 + (BN < 128 ? 1 : 0); ++t) {
+          const int c = t * 128 + 4 * lane;
+          if (c >= BN || tn * BN + c >= a.n) continue;
+          float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          float4 v[8];
+#pragma unroll
+          for (int peer = 0; peer < 8; ++peer)   // all the remote loads in flight together
+            v[peer] = peer < a.split
+                          ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(part, peer) + r * kPartLd + c)
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+          for (int peer = 0; peer < 8; ++peer) {
+            sum[0] += v[peer].x;
+            sum[1] += v[peer].y;
+            sum[2] += v[peer].z;
+            sum[3] += v[peer].w;
+          }
+          epilogue_quad<TOut>(a, sum, row, tn * BN + c);
+        }
+      }
+    }
+    cluster.sync();   // peers may still be reading this CTA's partial tile
   }
   tc_fence_before();
   __syncthreads();
@@ -349,16 +447,55 @@ bool MakeMap(CUtensorMap* map, int dtype, const void* base, int64_t inner, int64
 template <int BN, typename TOut>
 cudaError_t LaunchTc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, uint32_t idesc, int grid,
                      cudaStream_t stream) {
+  static_assert(BM * (BN + 4) * 4 <= Smem<BN>::kStages * Smem<BN>::kStageBytes, "partial tile must fit the ring");
   auto kernel = gemm_tc_kernel<BN, TOut>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN>::kTotal);
   if (e != cudaSuccess) return e;
   LaunchCfg lc;
-  lc.grid = dim3(grid);
+  lc.grid = dim3(grid, a.split, 1);
   lc.block = dim3(kThreads);
   lc.smem = Smem<BN>::kTotal;
   lc.stream = stream;
   lc.pdl = true;
+  lc.cluster_y = a.split;
   return Launch(lc, kernel, ma, mb, a, idesc);
+}
+
+// How many clusters of `split` CTAs of this kernel the device holds at once (a GPC takes
+// only whole clusters, so this can be well below SMs / split).  Cached per shape of launch.
+template <int BN, typename TOut>
+int ResidentClusters(int split) {
+  static std::mutex mu;
+  static int cached[9] = {0};
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[split] == 0) {
+    auto kernel = gemm_tc_kernel<BN, TOut>;
+    int n = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN>::kTotal) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(16, split, 1);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = Smem<BN>::kTotal;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 1;
+      attr.val.clusterDim.y = split;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) n = 0;
+      (void)cudaGetLastError();
+    }
+    cached[split] = n > 0 ? n : -1;
+  }
+  return cached[split] > 0 ? cached[split] : 0;
+}
+
+template <int BN>
+int ResidentClustersFor(int out_dtype, int split) {
+  if (out_dtype == B200_F32) return ResidentClusters<BN, float>(split);
+  if (out_dtype == B200_BF16) return ResidentClusters<BN, __nv_bfloat16>(split);
+  return ResidentClusters<BN, __half>(split);
 }
 
 }  // namespace
@@ -383,8 +520,29 @@ b200_status RunTcgen05(b200_context* ctx, cudaStream_t stream, const b200_gemm_p
   const int64_t m = p->m, n = p->n, k = p->k;
   // 128 x 256 tiles; narrower ones (128, 64 columns) when that is what it takes to spread
   // a few-row problem, which only streams B, over more SMs
-  const int64_t tiles_m = CeilDiv(m, BM);
-  const int bn = tiles_m * CeilDiv(n, 256) >= ctx->sm_count ? 256 : (tiles_m * CeilDiv(n, 128) >= ctx->sm_count ? 128 : 64);
+  const int64_t tiles_m = CeilDiv(m, BM), k_iters = CeilDiv(k, BK);
+  // Tile width and K split by a small cost model (microseconds).  A k step of a 128 x bn
+  // tile costs what the SM's share of L2 bandwidth or the MMAs take, whichever is longer
+  // (measured: 0.55 / 0.43 / 0.375 us for bn = 256 / 128 / 64); tiles run in waves over the
+  // SMs.  When the tiles leave SMs idle, a cluster of 2/4/8 CTAs splits one tile's K loop
+  // (a serial chain on one SM otherwise) and adds the partial tiles through distributed
+  // shared memory, for a fixed cost of the cluster barriers and the extra pass.
+  int bn = 256, split = 1;
+  double best = 1e30;
+  for (int cand : {256, 128, 64}) {
+    const double t_iter = cand == 256 ? 0.55 : (cand == 128 ? 0.43 : 0.375);
+    const int64_t tiles = tiles_m * CeilDiv(n, cand);
+    const double whole = static_cast<double>(CeilDiv(tiles, ctx->sm_count)) * k_iters * t_iter;
+    if (whole < best) best = whole, bn = cand, split = 1;
+    for (int sp = 2; sp <= 8; sp *= 2) {
+      if (tiles * sp > ctx->sm_count || k_iters / sp < 4) break;
+      const int resident = cand == 256 ? ResidentClustersFor<256>(p->c.dtype, sp)
+                                       : (cand == 128 ? ResidentClustersFor<128>(p->c.dtype, sp) : ResidentClustersFor<64>(p->c.dtype, sp));
+      if (tiles > resident) continue;   // a second wave of clusters would double the time
+      const double cost = static_cast<double>(CeilDiv(k_iters, sp)) * t_iter + 4.0;
+      if (cost < best) best = cost, bn = cand, split = sp;
+    }
+  }
   CUtensorMap ma, mb;
   bool ok;
   if (!ta) ok = MakeMap(&ma, p->a.dtype, p->a.ptr, k, m, p->a.ld, BK, BM);     // A [m][k]
@@ -408,9 +566,10 @@ b200_status RunTcgen05(b200_context* ctx, cudaStream_t stream, const b200_gemm_p
   a.tb = tb;
   a.tiles_m = static_cast<int>(tiles_m);
   a.tiles_n = static_cast<int>(CeilDiv(n, bn));
+  a.split = split;
   a.status = ctx->dev_status;
   const int64_t tiles = static_cast<int64_t>(a.tiles_m) * a.tiles_n;
-  const int grid = static_cast<int>(std::min<int64_t>(tiles, ctx->sm_count));
+  const int grid = split > 1 ? static_cast<int>(tiles) : static_cast<int>(std::min<int64_t>(tiles, ctx->sm_count));
   const uint32_t idesc = make_idesc(p->a.dtype == B200_BF16 ? 1 : 0, ta ? 1 : 0, tb ? 0 : 1, bn);
   cudaError_t e;
   const int out = p->c.dtype;

@@ -90,7 +90,7 @@ def bench_qmm(pkg, bits, m, n, k, buffers, reps, group=64):
             "rows_per_cta": plan[0], "split_k": plan[1]}
 
 
-def bench_gemm(pkg, m, n, k, act, bias, reps, dtype="bf16", transpose_b=False, buffers=4):
+def bench_gemm(pkg, m, n, k, act, bias, reps, dtype="bf16", transpose_b=False, buffers=4, route=0):
     import torch
     dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
     dev = "cuda"
@@ -98,18 +98,21 @@ def bench_gemm(pkg, m, n, k, act, bias, reps, dtype="bf16", transpose_b=False, b
     Bs = [torch.randn((n, k) if transpose_b else (k, n), device=dev).mul_(0.02).to(dt) for _ in range(buffers)]
     bias_t = torch.randn((n,), device=dev).mul_(0.01).to(dt) if bias else None
 
+    B = pkg.blas
+    outs = [torch.empty((m, n), dtype=dt, device=dev) for _ in range(buffers)]
+    prms = [B.GemmParams(m, n, k, B.Operand(a, k), B.Operand(b, b.stride(0), transpose=transpose_b), B.Operand(o, n))
+            for a, b, o in zip(As, Bs, outs)]
+    epi = B.SteelEpilogue(act, bias_t)
+
     def run():
-        for a, b in zip(As, Bs):
-            pkg.blas.matmul(a, b, bias=bias_t, act=act, transpose_b=transpose_b)
+        for prm in prms:
+            B.run_steel_gemm(prm, epi, route=route)
     sec = timed(run, reps) / buffers
     es = 4 if dtype == "f32" else 2
     flops = 2.0 * m * n * k
     nbytes = es * (m * k + k * n + m * n) + (es * n if bias else 0)
     hbm, tf, kind = peaks()
-    B = pkg.blas
-    d = torch.empty((m, n), dtype=dt, device=dev)
-    route = B.gemm_route(B.GemmParams(m, n, k, B.Operand(As[0], k), B.Operand(Bs[0], Bs[0].stride(0), transpose=transpose_b),
-                                      B.Operand(d, n)))
+    route = route or B.gemm_route(prms[0], epi)
     return {"op": "gemm", "dtype": dtype, "m": m, "n": n, "k": k, "act": act, "bias": bool(bias), "route": route,
             "us": sec * 1e6, "tflops": flops / sec / 1e12, f"frac_of_{kind}_tensor": flops / sec / 1e12 / tf,
             "frac_of_nominal_tensor": flops / sec / 1e12 / BF16_NOMINAL, "gbs": nbytes / sec / 1e9,
@@ -147,6 +150,7 @@ def main():
     ap.add_argument("--act", type=int, default=0)
     ap.add_argument("--bias", action="store_true")
     ap.add_argument("--tb", action="store_true")
+    ap.add_argument("--route", type=int, default=0, help="gemm: force a route (1 tcgen05, 2 few-row, 3 SIMT); 0 = the library's choice")
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--kind", default="softmax")
     ap.add_argument("--rows", type=int, default=8192)
@@ -156,7 +160,7 @@ def main():
         print(json.dumps(bench_qmm(pkg, a.bits, a.m, a.n, a.k, a.buffers, a.reps, a.group)), flush=True)
     elif a.op == "gemm":
         print(json.dumps(bench_gemm(pkg, a.m, a.n, a.k, a.act, a.bias, a.reps, a.dtype, a.tb,
-                                    max(4, min(a.buffers, int(512e6 // (a.n * a.k * 2)))))), flush=True)
+                                    max(4, min(a.buffers, int(512e6 // (a.n * a.k * 2)))), a.route)), flush=True)
     elif a.op == "rows":
         print(json.dumps(bench_rows(pkg, a.kind, a.rows, a.n, a.dtype, a.reps)), flush=True)
     else:

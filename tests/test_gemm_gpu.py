@@ -112,25 +112,12 @@ def test_few_row_route(vecs, vectors_are_b):
     p = pkg()
     m, n = (516 + 12, vecs) if vectors_are_b else (vecs, 516 + 12)
     for k in (1024, 576):
-        run_case(m, n, k, tb=True, route=0, bias=True, act=3, aux=True, seed=vecs)
+        run_case(m, n, k, tb=True, route=p._lib.ROUTE_FEWROW, bias=True, act=3, aux=True, seed=vecs)
     B_ = p.blas
     A, Bm, D = dev(np.zeros((m, 1024), bf16)), dev(np.zeros((n, 1024), bf16)), dev(np.zeros((m, n), bf16))
     prm = B_.GemmParams(m, n, 1024, B_.Operand(A, 1024), B_.Operand(Bm, 1024, transpose=True), B_.Operand(D, n))
-    assert B_.gemm_route(prm) == p._lib.ROUTE_FEWROW
-
-
-@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
-@pytest.mark.parametrize("dt_in,dt_out", [("bf16", "bf16"), ("f16", "f16"), ("bf16", "f32")])
-def test_few_row_nn_route(m, dt_in, dt_out):
-    """x . W with W stored [K][N]: the streaming kernel for the NN layout, every row
-    count class, ragged N and K, padded rows, all epilogue parts."""
-    p = pkg()
-    for n, k in ((520, 1024), (264, 777), (4096, 512)):
-        run_case(m, n, k, dt_in=dt_in, dt_out=dt_out, pad=8, bias=True, act=3, aux=True, alpha=0.5, seed=m)
-    B_ = p.blas
-    A, Bm, D = dev(np.zeros((m, 1024), bf16)), dev(np.zeros((1024, 520), bf16)), dev(np.zeros((m, 520), bf16))
-    prm = B_.GemmParams(m, 520, 1024, B_.Operand(A, 1024), B_.Operand(Bm, 520), B_.Operand(D, 520))
-    assert B_.gemm_route(prm) == p._lib.ROUTE_FEWROW
+    # up to 8 vectors the streaming kernel is the library's choice, above that the tensor-core route
+    assert B_.gemm_route(prm) == (p._lib.ROUTE_FEWROW if vecs <= 8 else p._lib.ROUTE_TCGEN05)
 
 
 def test_config1_f32_block():
@@ -223,6 +210,16 @@ def test_tcgen05_dtypes_and_epilogues(dt_in, dt_out):
     for act in (0, 1, 2, 3):
         _tc_case(160, 288, 192, dt_in=dt_in, dt_out=dt_out, act=act, bias=True, aux=(act % 2 == 1), seed=act)
     _tc_case(160, 288, 192, dt_in=dt_in, dt_out=dt_out, alpha=-0.5, beta=0.75)
+
+
+@pytest.mark.parametrize("dt_in,dt_out", [("bf16", "bf16"), ("f16", "f32")])
+def test_tcgen05_split_k_cluster(dt_in, dt_out):
+    """Few tiles and a long K: the K loop is split across a cluster of CTAs whose partial
+    tiles are added through distributed shared memory; every epilogue part, ragged K."""
+    for m, n, k in ((100, 200, 1000), (16, 520, 2048), (128, 1024, 4096), (7, 136, 8200)):
+        _tc_case(m, n, k, dt_in=dt_in, dt_out=dt_out, act=3, bias=True, aux=True, seed=k)
+        _tc_case(m, n, k, dt_in=dt_in, dt_out=dt_out, tb=True, alpha=-0.5, beta=0.75, seed=k + 1)
+    _tc_case(100, 200, 1000, dt_in=dt_in, dt_out=dt_out, ta=True, tb=True, act=1, seed=5)
 
 
 def test_tcgen05_many_tiles_persistent():
