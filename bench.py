@@ -278,6 +278,8 @@ def run_ours(args):
         from metal_pjrt_plugin_b200 import parallel
         tp = parallel.TensorParallel.from_torch_distributed(ctx)
         cfg_local = parallel.local_config(CFG, world)
+        if args.collective == "peer":   # sums over ranks as one kernel over peer memory
+            tp.connect_peers(args.batch * CFG["hidden"])
     B = args.batch
     params, cache = build_device_model(pkg, cfg_local, B, device, 4, world, rank, ctx)
     dec = pkg.qwen3.Decoder(params, cache, cfg_local, max_batch=B, ctx=ctx, tp=tp)
@@ -350,7 +352,7 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t_dev * 1e3 / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int4 weights, bf16 activations, f32 accumulate", "data": "synthetic",
-        "config": workload_config(B, world),
+        "config": dict(workload_config(B, world), **({"collective": args.collective} if world > 1 else {})),
         "e2e": {"value": B * args.steps / t_e2e, "unit": "tok/s", "h2d_bytes_per_step": int(tok_host.numel() * 4),
                 "d2h_bytes_per_step": int(logits_host.numel() * 4)},
         "gpu_launches": int(dec.launches_per_step(B) * args.steps),
@@ -382,6 +384,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--collective", default="nccl", choices=["peer", "nccl"],
+                    help="N > 1: the sums over ranks by the library's peer-memory kernel, or by ncclAllReduce")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

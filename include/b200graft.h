@@ -295,6 +295,23 @@ void b200_tp_destroy(b200_tp* tp);
 b200_status b200_tp_all_reduce_bf16(b200_tp* tp, b200_stream stream, void* buf, int64_t count);
 b200_status b200_tp_all_gather_f32(b200_tp* tp, b200_stream stream, const void* send, void* recv,
                                    int64_t count_per_rank);
+/* Peer exchange (optional; ranks are processes on GPUs of one NVLink domain, at most 8).
+ * The sum over ranks that follows a K-sharded projection is a few KB, so it is done by one
+ * kernel per rank over peer memory instead of a collective call: every rank allocates an
+ * exchange block (two slots of max_floats f32 + flags) and gets its CUDA IPC handle; the
+ * caller gathers the handles of all ranks (rank order, B200_TP_PEER_HANDLE_BYTES each) by
+ * any transport and connects, then synchronises the ranks on the host before first use
+ * and before b200_tp_destroy.  b200_tp_peer_partial(slot) is where the projection writes
+ * its f32 partial sums; consecutive exchanges must alternate slots 0, 1, 0, ...
+ * b200_tp_sum_residual_norm: x[batch, hidden] (bf16) += bf16(sum over ranks of the slot),
+ * h = rms_norm(x) * gain; peers are awaited with a bounded spin (B200_TIMEOUT through the
+ * context's status word). */
+#define B200_TP_PEER_HANDLE_BYTES 64
+b200_status b200_tp_peer_alloc(b200_tp* tp, int64_t max_floats, void* handle_out /* B200_TP_PEER_HANDLE_BYTES */);
+b200_status b200_tp_peer_connect(b200_tp* tp, const void* handles /* world x B200_TP_PEER_HANDLE_BYTES */);
+void* b200_tp_peer_partial(b200_tp* tp, int slot);
+b200_status b200_tp_sum_residual_norm(b200_tp* tp, b200_stream stream, int slot, void* x, const void* gain, void* h,
+                                      int64_t batch, int64_t hidden, double eps);
 
 #ifdef __cplusplus
 }

@@ -19,6 +19,7 @@ QMM_OUT_BF16, QMM_ADD_RESIDUAL, QMM_OUT_F32, QMM_OUT_F32_RAW = 0, 1, 2, 3
 QMM_PRO_NONE, QMM_PRO_RMSNORM, QMM_PRO_SILU_MUL = 0, 1, 2
 KIND_RMS, KIND_SOFTMAX, KIND_LOG_SOFTMAX, KIND_LAYERNORM = 0, 1, 2, 3
 TP_ID_BYTES = 128
+TP_PEER_HANDLE_BYTES = 64
 
 
 class B200Error(RuntimeError):
@@ -107,6 +108,10 @@ PROTOTYPES = {
     "b200_tp_destroy": (None, [_VP]),
     "b200_tp_all_reduce_bf16": (_I, [_VP, _VP, _VP, _I64]),
     "b200_tp_all_gather_f32": (_I, [_VP, _VP, _VP, _VP, _I64]),
+    "b200_tp_peer_alloc": (_I, [_VP, _I64, _VP]),
+    "b200_tp_peer_connect": (_I, [_VP, _VP]),
+    "b200_tp_peer_partial": (_VP, [_VP, _I]),
+    "b200_tp_sum_residual_norm": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _I64, _I64, C.c_double]),
 }
 
 _lib = None

@@ -134,6 +134,7 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   const int64_t E = c.hidden, HD = static_cast<int64_t>(c.heads) * c.head_dim;
   const int64_t QKV = static_cast<int64_t>(c.heads + 2 * c.kv_heads) * c.head_dim;
   const bool tp = d->tp != nullptr && d->tp->world > 1;
+  const bool peer = tp && d->tp->peer && static_cast<int64_t>(batch) * E <= d->tp->cap;
 
   // Up to 8 rows the RMSNorm in front of a projection is fused into its input
   // staging (h is never written); beyond that it is its own kernel.
@@ -151,7 +152,11 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
     B200_TRY(b200_attention_step(ctx, stream, d->qkv, L.q_norm, L.k_norm, d->inv_freq, L.k_cache, L.v_cache, d->attn,
                                  pos, d->attn_scratch, batch, c.heads, c.kv_heads, c.head_dim, c.max_len,
                                  c.rope_theta, c.rms_eps));
-    if (tp) {
+    if (tp && peer) {
+      // slot 0: the sum over ranks, the residual add and the next RMSNorm are one kernel over peer memory
+      B200_TRY(Qmm(d, stream, L.o, d->attn, TpPeerPartial(d->tp, 0), batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr));
+      B200_TRY(TpSumResidualNorm(d->tp, stream, 0, d->x, L.mlp_norm, d->h, batch, E, c.rms_eps));
+    } else if (tp) {
       B200_TRY(Qmm(d, stream, L.o, d->attn, d->y32, batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr));
       B200_TRY(TpAllReduce(d->tp, stream, d->y32, static_cast<int64_t>(batch) * E, B200_F32));
       B200_TRY(ResidualNorm(d, stream, L.mlp_norm, batch));
@@ -168,7 +173,11 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
                    nullptr));
     const void* next_norm = li + 1 < c.layers ? d->layers[li + 1].attn_norm : d->final_norm;
     // silu(gate) * up is fused into the staging of the down projection's input
-    if (tp) {
+    if (tp && peer) {
+      B200_TRY(Qmm(d, stream, L.down, d->gu, TpPeerPartial(d->tp, 1), batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr,
+                   B200_QMM_PRO_SILU_MUL));
+      B200_TRY(TpSumResidualNorm(d->tp, stream, 1, d->x, next_norm, d->h, batch, E, c.rms_eps));
+    } else if (tp) {
       B200_TRY(Qmm(d, stream, L.down, d->gu, d->y32, batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr,
                    B200_QMM_PRO_SILU_MUL));
       B200_TRY(TpAllReduce(d->tp, stream, d->y32, static_cast<int64_t>(batch) * E, B200_F32));

@@ -16,6 +16,7 @@ class TensorParallel:
         buf = (C.c_char * _lib.TP_ID_BYTES).from_buffer_copy(id_bytes)
         _lib.check(_lib.lib().b200_tp_create(self.ctx.handle, buf, rank, world, C.byref(handle)))
         self.handle = handle
+        self.peers_connected = False
 
     @staticmethod
     def make_id():
@@ -31,6 +32,36 @@ class TensorParallel:
         box = [cls.make_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         return cls(rank, world, box[0], ctx)
+
+    def connect_peers(self, max_floats):
+        """Allocates this rank's peer-exchange block (two slots of max_floats f32),
+        gathers every rank's CUDA IPC handle over torch.distributed, maps the
+        peers' blocks and synchronises the ranks.  After this the decoder's
+        sums over ranks run as one kernel over peer memory instead of NCCL."""
+        import torch.distributed as dist
+        buf = (C.c_char * _lib.TP_PEER_HANDLE_BYTES)()
+        _lib.check(_lib.lib().b200_tp_peer_alloc(self.handle, max_floats, buf))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(buf))
+        packed = (C.c_char * (_lib.TP_PEER_HANDLE_BYTES * self.world)).from_buffer_copy(b"".join(handles))
+        _lib.check(_lib.lib().b200_tp_peer_connect(self.handle, packed))
+        dist.barrier()
+        self.peers_connected = True
+
+    def peer_partial(self, slot, shape):
+        """This rank's slot (0/1) of the exchange block as an f32 tensor view."""
+        import torch
+        ptr = _lib.lib().b200_tp_peer_partial(self.handle, slot)
+        if not ptr:
+            raise RuntimeError("peer exchange is not connected")
+        iface = {"shape": tuple(shape), "typestr": "<f4", "data": (ptr, False), "version": 3}
+        holder = type("PeerSlot", (), {"__cuda_array_interface__": iface})()
+        return torch.as_tensor(holder, device=f"cuda:{self.ctx.device}")
+
+    def sum_residual_norm(self, slot, x, gain, h, eps=1e-6, stream=None):
+        """x += bf16(sum over ranks of slot), h = rms_norm(x) * gain (one kernel over peer memory)."""
+        _lib.check(_lib.lib().b200_tp_sum_residual_norm(self.handle, stream or _lib.current_stream(), slot, _lib.ptr(x),
+                                                        _lib.ptr(gain), _lib.ptr(h), x.shape[0], x.shape[1], eps))
 
     def all_reduce_bf16(self, t, stream=None):
         _lib.check(_lib.lib().b200_tp_all_reduce_bf16(self.handle, stream or _lib.current_stream(), _lib.ptr(t), t.numel()))

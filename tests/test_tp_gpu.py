@@ -12,7 +12,7 @@ from util import ROOT
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, out_q):
+def _worker(rank, world, port, out_q, peers):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -28,6 +28,8 @@ def _worker(rank, world, port, out_q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     ctx = pkg.Context(rank)
     tp = parallel.TensorParallel.from_torch_distributed(ctx)
+    if peers:   # the sums over ranks as one kernel over peer memory instead of NCCL
+        tp.connect_peers(4 * 256)
     cfg = inputs.decoder_config(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=512, vocab=1024)
     B, ctxlen, max_len = 3, 40, 64
     params, cache, tokens = inputs.config5(cfg, B, ctxlen, max_len=max_len)
@@ -40,7 +42,10 @@ def _worker(rank, world, port, out_q):
     pos = torch.tensor([ctxlen], dtype=torch.int32, device=device)
     logits = dec.step(tok, pos)
     logits2 = dec.step(tok, pos).clone()      # graph replay
+    for _ in range(20):                       # many exchanges: the slots and flags keep alternating
+        logits3 = dec.step(tok, pos)
     torch.cuda.synchronize()
+    assert torch.equal(logits3, logits2)
     status = ctx.error()
     got = host(logits)                                           # [world, B, V / world], rank-major
     got = np.concatenate([got[r] for r in range(world)], axis=-1)
@@ -56,15 +61,16 @@ def _worker(rank, world, port, out_q):
     dist.destroy_process_group()
 
 
-def test_tp2_decoder_matches_oracle():
+@pytest.mark.parametrize("peers", [False, True])
+def test_tp2_decoder_matches_oracle(peers):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = 29500 + os.getpid() % 2000 + (7 if peers else 0)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peers)) for r in range(2)]
     for p_ in procs:
         p_.start()
     res = dict(q.get(timeout=300) for _ in range(2))
