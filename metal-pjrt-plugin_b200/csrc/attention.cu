@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
 // Merges the partials of one (batch, query head): out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s.
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads) attn_combine_kernel(const AttnArgs a) {
-  extern __shared__ float wsm[];   // [splits] weights e^{m_s - M}
+  extern __shared__ float wsm[];   // [2][splits]: weights e^{m_s - M}, then the partial sums l_s
   __shared__ float red[kThreads / 32];
   pdl_wait();
   pdl_launch_dependents();
@@ -275,11 +275,19 @@ __global__ void __launch_bounds__(kThreads) attn_combine_kernel(const AttnArgs a
   const int nsplit = (n_valid + kChunk - 1) / kChunk;
   const float* base = a.scratch + (static_cast<int64_t>(b) * a.kv_heads + kv) * a.splits * G * (D + 2) + gq * (D + 2);
   const int64_t stride = static_cast<int64_t>(G) * (D + 2);
+  // Everything this thread needs from the partials is requested at once (one trip to L2):
+  // its output dimension of the first kPre splits, and the (max, sum) pair of split `tid`.
+  constexpr int kPre = 40;
+  const int d0 = tid < D ? tid : 0;
+  float o[kPre];
+#pragma unroll
+  for (int s = 0; s < kPre; ++s) o[s] = s < nsplit ? base[s * stride + d0] : 0.0f;
   float m = -INFINITY;
   for (int s = tid; s < nsplit; s += kThreads) {
-    const float ms = base[s * stride + D];
-    wsm[s] = ms;
-    m = fmaxf(m, ms);
+    const float2 ml = *reinterpret_cast<const float2*>(&base[s * stride + D]);
+    wsm[s] = ml.x;
+    wsm[a.splits + s] = ml.y;
+    m = fmaxf(m, ml.x);
   }
   m = warp_max(m);
   if (lane == 0) red[warp] = m;
@@ -290,7 +298,7 @@ __global__ void __launch_bounds__(kThreads) attn_combine_kernel(const AttnArgs a
   for (int s = tid; s < nsplit; s += kThreads) {
     const float w = expf(wsm[s] - m);
     wsm[s] = w;
-    den = fmaf(w, base[s * stride + D + 1], den);
+    den = fmaf(w, wsm[a.splits + s], den);
   }
   den = warp_sum(den);
   if (lane == 0) red[warp] = den;
@@ -298,8 +306,15 @@ __global__ void __launch_bounds__(kThreads) attn_combine_kernel(const AttnArgs a
   den = (red[0] + red[1]) + (red[2] + red[3]);
   for (int d = tid; d < D; d += kThreads) {
     float num = 0.0f;
+    if (d == d0) {
+#pragma unroll
+      for (int s = 0; s < kPre; ++s)
+        if (s < nsplit) num = fmaf(wsm[s], o[s], num);
+    } else {
+      for (int s = 0; s < min(nsplit, kPre); ++s) num = fmaf(wsm[s], base[s * stride + d], num);
+    }
 #pragma unroll 8
-    for (int s = 0; s < nsplit; ++s) num = fmaf(wsm[s], base[s * stride + d], num);
+    for (int s = kPre; s < nsplit; ++s) num = fmaf(wsm[s], base[s * stride + d], num);
     a.out[(static_cast<int64_t>(b) * a.heads + h) * D + d] = __float2bfloat16_rn(num / den);
   }
 }
@@ -321,7 +336,7 @@ b200_status LaunchAttn(b200_context* ctx, cudaStream_t stream, const AttnArgs& a
   }
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "attention launch: %s", cudaGetErrorString(e)));
   lc.grid = dim3(a.heads, static_cast<unsigned>(batch));
-  lc.smem = static_cast<size_t>(a.splits) * sizeof(float);
+  lc.smem = static_cast<size_t>(2 * a.splits) * sizeof(float);
   switch (group) {
     case 1: e = Launch(lc, attn_combine_kernel<D, 1>, a); break;
     case 2: e = Launch(lc, attn_combine_kernel<D, 2>, a); break;

@@ -15,6 +15,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstring>
 
 #include "tp.cuh"
@@ -95,8 +96,8 @@ __device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* p) {
   return v;
 }
 
-// One CTA per batch row, 256 threads, n a multiple of 4.
-__global__ void __launch_bounds__(256) peer_sum_residual_norm_kernel(const PeerArgs a) {
+// One CTA per batch row, up to 1024 threads (a float4 of every rank's partial each), n a multiple of 4.
+__global__ void __launch_bounds__(1024) peer_sum_residual_norm_kernel(const PeerArgs a) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
   __shared__ uint32_t seq_s;
@@ -127,22 +128,32 @@ __global__ void __launch_bounds__(256) peer_sum_residual_norm_kernel(const PeerA
   const int64_t base = static_cast<int64_t>(blockIdx.x) * a.n;
   float ss = 0.0f;
   for (int i = tid * 4; i < a.n; i += blockDim.x * 4) {
+    // every rank's four values requested before any is used (one NVLink round trip, not `world`)
+    float4 v[kTpMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r)
+      v[r] = r < a.world ? ld_relaxed_sys_f4(a.partial[r] + base + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const uint2 xraw = *reinterpret_cast<const uint2*>(a.x + base + i);
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int r = 0; r < a.world; ++r) {   // rank order on every rank: identical sums everywhere
-      const float4 v = ld_relaxed_sys_f4(a.partial[r] + base + i);
-      acc.x += v.x;
-      acc.y += v.y;
-      acc.z += v.z;
-      acc.w += v.w;
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r) {   // rank order on every rank: identical sums everywhere
+      if (r < a.world) {
+        acc.x += v[r].x;
+        acc.y += v[r].y;
+        acc.z += v[r].z;
+        acc.w += v[r].w;
+      }
     }
     const float y[4] = {acc.x, acc.y, acc.z, acc.w};
+    const float xo[4] = {bf16_lo(xraw.x), bf16_hi(xraw.x), bf16_lo(xraw.y), bf16_hi(xraw.y)};
+    float o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float v = bf16_round(__bfloat162float(a.x[base + i + j]) + bf16_round(y[j]));
-      row[i + j] = v;
-      a.x[base + i + j] = __float2bfloat16_rn(v);
-      ss = fmaf(v, v, ss);
+      o[j] = bf16_round(xo[j] + bf16_round(y[j]));
+      row[i + j] = o[j];
+      ss = fmaf(o[j], o[j], ss);
     }
+    *reinterpret_cast<uint2*>(a.x + base + i) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
   }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) scratch[tid >> 5] = ss;
@@ -212,7 +223,8 @@ b200_status TpSumResidualNorm(b200_tp* tp, cudaStream_t stream, int slot, void* 
   if (slot < 0 || slot > 1 || batch < 1 || hidden < 4 || hidden % 4 != 0 || batch * hidden > tp->cap)
     return Fail(B200_INVALID_ARGUMENT, "peer exchange: batch %lld x hidden %lld does not fit (capacity %lld floats, hidden %% 4)",
                 static_cast<long long>(batch), static_cast<long long>(hidden), static_cast<long long>(tp->cap));
-  if (x == nullptr || gain == nullptr || h == nullptr) return Fail(B200_INVALID_ARGUMENT, "peer exchange: null buffer");
+  if (x == nullptr || gain == nullptr || h == nullptr || !Aligned(x, 8))
+    return Fail(B200_INVALID_ARGUMENT, "peer exchange: null or misaligned buffer");
   PeerArgs a = {};
   for (int r = 0; r < tp->world; ++r) {
     a.partial[r] = static_cast<const float*>(tp->peer_block[r]) + static_cast<int64_t>(slot) * tp->cap;
@@ -231,7 +243,7 @@ b200_status TpSumResidualNorm(b200_tp* tp, cudaStream_t stream, int slot, void* 
   a.status = tp->ctx->dev_status;
   LaunchCfg lc;
   lc.grid = dim3(static_cast<unsigned>(batch));
-  lc.block = dim3(256);
+  lc.block = dim3(static_cast<unsigned>(std::min<int64_t>(1024, (hidden / 4 + 31) / 32 * 32)));
   lc.smem = static_cast<size_t>(hidden) * sizeof(float);
   lc.stream = stream;
   lc.pdl = true;
