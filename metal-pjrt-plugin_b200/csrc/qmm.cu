@@ -384,7 +384,13 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     scale_load(static_cast<int>(blockIdx.x) * R);
     scale_store(static_cast<int>(blockIdx.x) * R, so);
     pdl_wait();  // x (and the residual) come from the previous kernel
-    if (a.prologue == B200_QMM_PRO_RMSNORM) {
+    // RMSNorm in one pass: when every thread stages at most one 16-input unit of a whole row
+    // (M * K <= 8192) and warps do not straddle rows, the sum of squares comes from the
+    // values the threads hold for staging anyway (one trip to L2, one barrier).
+    const int units_all = a.M * groups_cta * 4;
+    const bool rms_one_pass = a.prologue == B200_QMM_PRO_RMSNORM && solo && units_all <= kConsumerThreads &&
+                              (groups_cta * 4) % 32 == 0;
+    if (a.prologue == B200_QMM_PRO_RMSNORM && !rms_one_pass) {
       // 1 / rms of every full row of x (M <= 8), recomputed by each CTA
       float ss[8];
 #pragma unroll
@@ -423,8 +429,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     }
     // Stage x in register order: unit (m, group, t) = 16 inputs = two runs of 8 (or one of 16).
     {
-      const int units = a.M * groups_cta * 4;
-      const int units_pad = (units + 31) & ~31;
+      const int units = units_all;
+      // one pass: every consumer thread runs the body exactly once (it holds a barrier)
+      const int units_pad = rms_one_pass ? kConsumerThreads : (units + 31) & ~31;
       constexpr bool kOneRun = FMT == kInt4Seq || FMT == kInt8;
       for (int u = tid; u < units_pad; u += kConsumerThreads) {
         const bool valid = u < units;
@@ -432,12 +439,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         const int ug = (u >> 2) % groups_cta;
         const int um = (u >> 2) / groups_cta;
         float sum = 0.0f;
-        if (valid) {
-          const int kbase = k_begin + ug * kGroupK;
-          const int run0 = kOneRun ? 16 * ut : 8 * ut;
-          const int run1 = kOneRun ? 16 * ut + 8 : 32 + 8 * ut;
-          float e[16];
-          auto load_run = [&](const __nv_bfloat16* base, int k, float* dst) {
+        float e[16], gn[16];
+        const int kbase = k_begin + ug * kGroupK;
+        const int run0 = kOneRun ? 16 * ut : 8 * ut;
+        const int run1 = kOneRun ? 16 * ut + 8 : 32 + 8 * ut;
+        auto load_run = [&](const __nv_bfloat16* base, int k, float* dst) {
             if (a.x_vec) {
               const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + k));
               const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -451,13 +457,35 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
               for (int j = 0; j < 8; ++j) dst[j] = ldg_bf16(base + k + j);
             }
           };
-          const __nv_bfloat16* xr = a.x + static_cast<size_t>(um) * a.ldx;
+        const __nv_bfloat16* xr = a.x + static_cast<size_t>(valid ? um : 0) * a.ldx;
+        if (valid) {
           load_run(xr, kbase + run0, e);
           load_run(xr, kbase + run1, e + 8);
           if (a.prologue == B200_QMM_PRO_RMSNORM) {
-            float gn[16];
             load_run(a.gain, kbase + run0, gn);
             load_run(a.gain, kbase + run1, gn + 8);
+          }
+        }
+        if (rms_one_pass) {
+          float ss = 0.0f;
+          if (valid) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ss = fmaf(e[j], e[j], ss);
+          }
+          ss = warp_sum(ss);
+          if (lane == 0) ss_part[warp][0] = ss;
+          consumer_barrier();
+          if (valid) {
+            const int wpr = groups_cta * 4 / 32;   // warps per row of x
+            float tsum = 0.0f;
+            for (int w = um * wpr; w < (um + 1) * wpr; ++w) tsum += ss_part[w][0];
+            const float rr = 1.0f / sqrtf(tsum / static_cast<float>(a.K) + a.eps);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) e[j] = bf16_round((e[j] * rr) * gn[j]);
+          }
+        }
+        if (valid) {
+          if (a.prologue == B200_QMM_PRO_RMSNORM && !rms_one_pass) {
             const float rr = rinv[um];
 #pragma unroll
             for (int j = 0; j < 16; ++j) e[j] = bf16_round((e[j] * rr) * gn[j]);
@@ -468,7 +496,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             load_run(xr + a.K, kbase + run1, up + 8);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float sig = bf16_round(1.0f / (1.0f + expf(-e[j])));
+              // hardware exp2 / reciprocal: their error (~1e-6 relative) sits far below the bf16
+              // rounding that follows, and the accurate forms cost 3 us per launch here
+              const float sig = bf16_round(__fdividef(1.0f, 1.0f + __expf(-e[j])));
               e[j] = bf16_round(bf16_round(e[j] * sig) * up[j]);
             }
           }

@@ -54,7 +54,7 @@ def timed(fn, reps, warmup=3, graph=True):
     return a.elapsed_time(b) * 1e-3 / reps
 
 
-def bench_qmm(pkg, bits, m, n, k, buffers, reps, group=64):
+def bench_qmm(pkg, bits, m, n, k, buffers, reps, group=64, fuse=""):
     import torch
     dev = "cuda"
     ws = []
@@ -69,11 +69,13 @@ def bench_qmm(pkg, bits, m, n, k, buffers, reps, group=64):
                        "s": torch.full((n, k // g), 0.001, dtype=torch.bfloat16, device=dev)})
         else:
             ws.append(torch.randn((n, k), device=dev).mul_(0.02).to(torch.bfloat16))
-    x = torch.randn((m, k), device=dev).to(torch.bfloat16)
+    x = torch.randn((m, 2 * k if fuse == "silu" else k), device=dev).to(torch.bfloat16)
+    gain = torch.ones((k,), device=dev, dtype=torch.bfloat16) if fuse == "rms" else None
+    res = torch.zeros((m, n), device=dev, dtype=torch.bfloat16) if fuse in ("res", "silu") else None
 
     def run():
         for w in ws:
-            pkg.qwen3.linear(x, w)
+            pkg.qwen3.linear(x, w, rms_gain=gain, silu_mul=fuse == "silu", residual=res)
     sec = timed(run, reps) / buffers
     if bits == 4:
         nbytes = n * k * 0.5625
@@ -150,6 +152,8 @@ def main():
     ap.add_argument("--act", type=int, default=0)
     ap.add_argument("--bias", action="store_true")
     ap.add_argument("--tb", action="store_true")
+    ap.add_argument("--fuse", default="", choices=["", "rms", "silu", "res"],
+                    help="qmm: fused RMSNorm prologue / silu(gate)*up prologue + residual / residual epilogue")
     ap.add_argument("--route", type=int, default=0, help="gemm: force a route (1 tcgen05, 2 few-row, 3 SIMT); 0 = the library's choice")
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--kind", default="softmax")
@@ -157,7 +161,7 @@ def main():
     a = ap.parse_args()
     pkg = load_package()
     if a.op == "qmm":
-        print(json.dumps(bench_qmm(pkg, a.bits, a.m, a.n, a.k, a.buffers, a.reps, a.group)), flush=True)
+        print(json.dumps(bench_qmm(pkg, a.bits, a.m, a.n, a.k, a.buffers, a.reps, a.group, a.fuse)), flush=True)
     elif a.op == "gemm":
         print(json.dumps(bench_gemm(pkg, a.m, a.n, a.k, a.act, a.bias, a.reps, a.dtype, a.tb,
                                     max(4, min(a.buffers, int(512e6 // (a.n * a.k * 2)))), a.route)), flush=True)
