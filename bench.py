@@ -384,7 +384,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--collective", default="nccl", choices=["peer", "nccl"],
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the sums over ranks by the library's peer-memory kernel, or by ncclAllReduce")
     args = ap.parse_args()
     if args.impl == "reference":
