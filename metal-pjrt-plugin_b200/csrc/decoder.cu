@@ -71,8 +71,7 @@ struct b200_decoder {
   const void* lm_head = nullptr;
   b200_tp* tp = nullptr;
   // activations (device, sized for max_batch)
-  __nv_bfloat16 *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr,
-                *act = nullptr;
+  __nv_bfloat16 *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr;
   float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr, *inv_freq = nullptr;
   bool use_graph = true;
   cudaStream_t capture_stream = nullptr;  // graphs are captured here (the caller's stream may be the legacy one)
@@ -248,10 +247,8 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
   cudaError_t e = Alloc(&d->x, B * c.hidden);
   if (e == cudaSuccess) e = Alloc(&d->h, B * c.hidden);
   if (e == cudaSuccess) e = Alloc(&d->qkv, B * qkv);
-  if (e == cudaSuccess) e = Alloc(&d->q, B * c.heads * c.head_dim);
   if (e == cudaSuccess) e = Alloc(&d->attn, B * c.heads * c.head_dim);
   if (e == cudaSuccess) e = Alloc(&d->gu, B * 2 * c.inter);
-  if (e == cudaSuccess) e = Alloc(&d->act, B * static_cast<size_t>(c.inter));
   if (e == cudaSuccess) e = Alloc(&d->y32, B * c.hidden);
   if (e == cudaSuccess)
     e = cudaMalloc(reinterpret_cast<void**>(&d->attn_scratch),
@@ -280,8 +277,8 @@ void b200_decoder_destroy(b200_decoder* d) {
   for (auto& kv : d->graphs) cudaGraphExecDestroy(kv.second);
   if (d->capture_stream != nullptr) cudaStreamDestroy(d->capture_stream);
   for (void* p : {static_cast<void*>(d->x), static_cast<void*>(d->h), static_cast<void*>(d->qkv),
-                  static_cast<void*>(d->q), static_cast<void*>(d->attn), static_cast<void*>(d->gu),
-                  static_cast<void*>(d->act), static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
+                  static_cast<void*>(d->attn), static_cast<void*>(d->gu),
+                  static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
                   static_cast<void*>(d->logits_local), static_cast<void*>(d->inv_freq)})
     if (p != nullptr) cudaFree(p);
   delete d;

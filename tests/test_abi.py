@@ -148,3 +148,14 @@ def test_no_device_means_a_loud_failure():
     with pytest.raises(p.B200Error) as e:
         p.Context(0)
     assert e.value.status == p._lib.FAILED_PRECONDITION and "no CPU fallback" in str(e.value)
+
+
+def test_peer_exchange_rejects_bad_arguments():
+    """The peer-exchange entry points validate before touching a device."""
+    p = pkg()
+    L, lib = p._lib, p.lib()
+    buf = (C.c_char * L.TP_PEER_HANDLE_BYTES)()
+    assert lib.b200_tp_peer_alloc(None, 1024, buf) == L.INVALID_ARGUMENT
+    assert lib.b200_tp_peer_connect(None, buf) == L.INVALID_ARGUMENT
+    assert not lib.b200_tp_peer_partial(None, 0)
+    assert lib.b200_tp_sum_residual_norm(None, None, 0, None, None, None, 1, 64, 1e-6) == L.FAILED_PRECONDITION
