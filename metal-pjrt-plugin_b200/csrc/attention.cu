@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
   constexpr int HALF = D / 2;
   constexpr int KV4 = HALF / 8;   // 16-byte loads of K per thread (two threads per position)
   __shared__ __align__(16) float qs[G][2][HALF + 4];
-  __shared__ float sc[G][kChunk];
+  __shared__ __align__(16) float sc[G][kChunk];
   __shared__ float red[G][kThreads / 32];
   __shared__ float knew[2][HALF + 4];
   __shared__ float vnew[D];
@@ -233,13 +233,27 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
 #pragma unroll
       for (int j = 0; j < kChunk / 8; ++j) {
         const uint32_t w[4] = {vreg[j].x, vreg[j].y, vreg[j].z, vreg[j].w};
+        float v[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int s = 8 * j + e;
-          float v = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
-          if (s0 + s >= n_old) v = (owner && s0 + s == pos) ? vnew[tid] : 0.0f;
+          v[e] = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+          if (s0 + s >= n_old) v[e] = (owner && s0 + s == pos) ? vnew[tid] : 0.0f;
+        }
+        // the eight probabilities of a head as two 16-byte broadcast reads (the loop is bound by
+        // shared-memory instructions otherwise: one scalar read per multiply-add)
 #pragma unroll
-          for (int gq = 0; gq < G; ++gq) acc[gq] = fmaf(sc[gq][s], v, acc[gq]);
+        for (int gq = 0; gq < G; ++gq) {
+          const float4 p0 = *reinterpret_cast<const float4*>(&sc[gq][8 * j]);
+          const float4 p1 = *reinterpret_cast<const float4*>(&sc[gq][8 * j + 4]);
+          acc[gq] = fmaf(p0.x, v[0], acc[gq]);
+          acc[gq] = fmaf(p0.y, v[1], acc[gq]);
+          acc[gq] = fmaf(p0.z, v[2], acc[gq]);
+          acc[gq] = fmaf(p0.w, v[3], acc[gq]);
+          acc[gq] = fmaf(p1.x, v[4], acc[gq]);
+          acc[gq] = fmaf(p1.y, v[5], acc[gq]);
+          acc[gq] = fmaf(p1.z, v[6], acc[gq]);
+          acc[gq] = fmaf(p1.w, v[7], acc[gq]);
         }
       }
     } else {

@@ -272,12 +272,12 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   size_t off = (static_cast<size_t>(2 * NS) * 8 + 127) & ~static_cast<size_t>(127);
   // Cross-warp reduction buffer.  Small tiles (one MMA row tile, batch <= 8) without a
   // split of K: every warp stores its partial tile, [2][warps][R][MP], and the
-  // epilogue threads add the 16 partials.  Otherwise: [2][R][MP] added into atomically
-  // (with K split across a cluster, the tile the peers read through distributed shared memory).
+  // epilogue threads add the 16 partials.  Otherwise: [2][R][MP] added into atomically; with
+  // K split across a cluster [4][R][MP], the tiles the peers read through distributed shared memory.
   constexpr bool kPartials = MB == 1;
   const bool partials = kPartials && solo;
   float* red = reinterpret_cast<float*>(smem + off);
-  off += static_cast<size_t>(2) * R * MP * 4 * (kPartials ? kConsumerWarps : 1);
+  off += static_cast<size_t>(kPartials ? 2 * kConsumerWarps : 4) * R * MP * 4;
   float* xsum = reinterpret_cast<float*>(smem + off);                // [groups_cta][MP]
   off += (static_cast<size_t>(groups_cta) * MP * 4 + 127) & ~static_cast<size_t>(127);
   uint4* xs = reinterpret_cast<uint4*>(smem + off);                  // [groups_cta][2][M][4] x 16 B
@@ -288,19 +288,18 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   uint8_t* stage_base = smem + off;
   __shared__ float ss_part[kConsumerWarps][8];
   __shared__ float rinv[8];
-  __shared__ __align__(8) uint64_t tile_bar[2];   // K split: "every CTA of the cluster has finished tile ti"
+  __shared__ __align__(8) uint64_t tile_bar[4];   // K split: "every CTA of the cluster has finished tile ti" (ti mod 4)
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kConsumerWarps);
     }
-    mbar_init(&tile_bar[0], split);
-    mbar_init(&tile_bar[1], split);
+    for (int i = 0; i < 4; ++i) mbar_init(&tile_bar[i], split);
     mbar_fence_init();
   }
   if (!partials)
-    for (int i = tid; i < 2 * R * MP; i += kThreads) red[i] = 0.0f;
+    for (int i = tid; i < (solo ? 2 : 4) * R * MP; i += kThreads) red[i] = 0.0f;
   for (int i = tid; i < groups_cta * MP; i += kThreads) xsum[i] = 0.0f;
   __syncthreads();
   if (!solo) cg::this_cluster().sync();   // the peers' barriers exist before anyone arrives on them
@@ -654,15 +653,67 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       }
     }
 
-    // Consumer threads only.  Caller has passed consumer_barrier(), so the CTA's adds into
-    // the tile's buffer are ordered before thread 0's release-arrivals.
-    auto cluster_tile_barrier = [&](int ti) {
-      uint64_t* bar = &tile_bar[ti & 1];
+    // K split across the cluster (consumer threads only).  Tile ti of every CTA lands in buffer
+    // ti mod 4 of its own shared memory.  After its adds (and a consumer_barrier, which orders
+    // them before thread 0's release-arrivals) a CTA arrives on barrier ti mod 4 of every peer;
+    // it finishes its share of tile ti's rows from all peers' buffers one tile LATER, when the
+    // peers' arrivals are long there, so nobody waits for the slowest CTA tile by tile.
+    auto cluster_arrive = [&](int ti) {
       if (tid == 0)
-        for (int c = 0; c < split; ++c) mbar_arrive_cluster(bar, static_cast<uint32_t>(c));
-      if (!dead && !mbar_wait_bounded_cluster(bar, static_cast<uint32_t>(ti >> 1) & 1u)) {
-        report_timeout(a.status, 300 + (ti & 1));
+        for (int c = 0; c < split; ++c) mbar_arrive_cluster(&tile_bar[ti & 3], static_cast<uint32_t>(c));
+    };
+    auto cluster_wait = [&](int ti) {
+      if (!dead && !mbar_wait_bounded_cluster(&tile_bar[ti & 3], static_cast<uint32_t>(ti >> 2) & 1u)) {
+        report_timeout(a.status, 300 + (ti & 3));
         dead = true;
+      }
+    };
+    auto cluster_finish = [&](int ti) {
+      const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
+      const int rows_valid = min(R, a.N - n0);
+      const float* tile = red + (ti & 3) * R * MP;
+      cluster_wait(ti);
+      const int rows_per_rank = (R + split - 1) / split;
+      const int r_begin = static_cast<int>(blockIdx.y) * rows_per_rank;
+      const int r_count = min(min(r_begin + rows_per_rank, R), rows_valid) - r_begin;
+      if (r_count <= 0 || dead) return;
+      cg::cluster_group cluster = cg::this_cluster();
+      // adjacent threads read adjacent words of the peers' tiles ([row][batch], batch fastest);
+      // four batch columns per thread and read when the batch allows it
+      if (a.M % 4 == 0) {
+        const int mq = a.M / 4;
+        for (int idx = tid; idx < r_count * mq; idx += kConsumerThreads) {
+          const int r = r_begin + idx / mq, m = (idx % mq) * 4;
+          float4 part[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            part[c] = c < split ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, c) + r * MP + m)
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            v.x += part[c].x;
+            v.y += part[c].y;
+            v.z += part[c].z;
+            v.w += part[c].w;
+          }
+          store_output<FMT, GROUPED>(a, v.x, m, n0 + r);
+          store_output<FMT, GROUPED>(a, v.y, m + 1, n0 + r);
+          store_output<FMT, GROUPED>(a, v.z, m + 2, n0 + r);
+          store_output<FMT, GROUPED>(a, v.w, m + 3, n0 + r);
+        }
+        return;
+      }
+      for (int idx = tid; idx < r_count * a.M; idx += kConsumerThreads) {
+        const int r = r_begin + idx / a.M, m = idx % a.M;
+        float part[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)   // all the remote reads in flight together
+          part[c] = c < split ? cluster.map_shared_rank(tile, c)[r * MP + m] : 0.0f;
+        float v = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v += part[c];
+        store_output<FMT, GROUPED>(a, v, m, n0 + r);
       }
     };
 
@@ -670,7 +721,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
       const int rows_valid = min(R, a.N - n0);
       const float2* so_cur = so + (ti & 1) * so_buf;
-      float* red_cur = red + (ti & 1) * R * MP * (partials ? kConsumerWarps : 1);
+      float* red_cur = solo ? red + (ti & 1) * R * MP * (partials ? kConsumerWarps : 1) : red + (ti & 3) * R * MP;
       const bool has_next = ti + 1 < n_my;
       if (has_next) scale_load(n0 + static_cast<int>(gridDim.x) * R);
 
@@ -764,32 +815,24 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
           }
         }
       } else {
-        // K split across the cluster: tell every CTA this one's tile is complete, wait for
-        // all of theirs, then finish this CTA's share of the rows from the peers' tiles.
-        cluster_tile_barrier(ti);
-        const int rows_per_rank = (R + split - 1) / split;
-        const int r_begin = static_cast<int>(blockIdx.y) * rows_per_rank;
-        const int r_count = min(min(r_begin + rows_per_rank, R), rows_valid) - r_begin;
-        if (r_count > 0 && !dead) {
-          cg::cluster_group cluster = cg::this_cluster();
-          for (int idx = tid; idx < r_count * a.M; idx += kConsumerThreads) {
-            const int r = r_begin + idx % r_count, m = idx / r_count;
-            float v = 0.0f;
-            for (int c = 0; c < split; ++c) v += cluster.map_shared_rank(red_cur, c)[r * MP + m];
-            store_output<FMT, GROUPED>(a, v, m, n0 + r);
-          }
-        }
-        // The peers finished reading the previous tile's buffer before they arrived for
-        // this one: clear it for the tile after this.
-        if (ti > 0) {
-          float* prev = red + ((ti + 1) & 1) * R * MP;
-          for (int i = tid; i < R * MP; i += kConsumerThreads) prev[i] = 0.0f;
+        cluster_arrive(ti);
+        if (ti > 0) cluster_finish(ti - 1);
+        // Buffer (ti + 1) mod 4 held tile ti - 3.  Every peer read it before arriving for tile
+        // ti - 1, which this CTA has just waited for: clear it for tile ti + 1.
+        if (ti >= 3) {
+          float* next = red + ((ti + 1) & 3) * R * MP;
+          for (int i = tid; i < R * MP; i += kConsumerThreads) next[i] = 0.0f;
         }
         consumer_barrier();
       }
     }
-    // no CTA leaves while a peer may still read its last tile
-    if (!solo) cluster_tile_barrier(n_my);
+    if (!solo) {
+      cluster_finish(n_my - 1);
+      // no CTA leaves while a peer may still read its last tiles
+      consumer_barrier();
+      cluster_arrive(n_my);
+      cluster_wait(n_my);
+    }
   }
 }
 
@@ -811,7 +854,7 @@ int ChunkK(int fmt, int mb, int rt) { return ChunkRowBytes(mb, rt) * 8 / BitsOf(
 size_t SmemFor(const Plan& pl, int M, int k_per_cta) {
   const int R = 16 * pl.rt, MP = 8 * pl.mb, groups = k_per_cta / kGroupK;
   size_t off = (static_cast<size_t>(2 * pl.stages) * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(2) * R * MP * 4 * (pl.mb == 1 ? kConsumerWarps : 1);
+  off += static_cast<size_t>(pl.mb == 1 ? 2 * kConsumerWarps : 4) * R * MP * 4;
   off += (static_cast<size_t>(groups) * MP * 4 + 127) & ~static_cast<size_t>(127);
   off += (static_cast<size_t>(groups) * M * 128 + 127) & ~static_cast<size_t>(127);
   if (pl.grouped) off += (static_cast<size_t>(2) * groups * R * 8 + 127) & ~static_cast<size_t>(127);
