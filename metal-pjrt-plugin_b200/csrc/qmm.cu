@@ -245,6 +245,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   using F = Fmt<FMT>;
   constexpr int R = 16 * RT;
   constexpr int MP = 8 * MB;
+  // Row pitch of the tiles that are added into atomically: above one batch block, four words
+  // more than the batch width, so that the eight rows a warp adds into fall in different banks.
+  constexpr int RP = MB > 1 ? MP + 4 : MP;
   // One pipeline stage holds R rows x kChunkK inputs; a row's share arrives as ONE
   // bulk copy (small copies are bound by the copy engine's request rate, not by HBM).
   constexpr int kChunkRowBytes = MB == 1 ? kCopyBytes : kCopyBytes / RT;
@@ -277,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   constexpr bool kPartials = MB == 1;
   const bool partials = kPartials && solo;
   float* red = reinterpret_cast<float*>(smem + off);
-  off += static_cast<size_t>(kPartials ? 2 * kConsumerWarps : 4) * R * MP * 4;
+  off += static_cast<size_t>(kPartials ? 2 * kConsumerWarps * MP : 4 * RP) * R * 4;
   float* xsum = reinterpret_cast<float*>(smem + off);                // [groups_cta][MP]
   off += (static_cast<size_t>(groups_cta) * MP * 4 + 127) & ~static_cast<size_t>(127);
   uint4* xs = reinterpret_cast<uint4*>(smem + off);                  // [groups_cta][2][M][4] x 16 B
@@ -299,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     mbar_fence_init();
   }
   if (!partials)
-    for (int i = tid; i < (solo ? 2 : 4) * R * MP; i += kThreads) red[i] = 0.0f;
+    for (int i = tid; i < (solo ? 2 : 4) * R * RP; i += kThreads) red[i] = 0.0f;
   for (int i = tid; i < groups_cta * MP; i += kThreads) xsum[i] = 0.0f;
   __syncthreads();
   if (!solo) cg::this_cluster().sync();   // the peers' barriers exist before anyone arrives on them
@@ -671,7 +674,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     auto cluster_finish = [&](int ti) {
       const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
       const int rows_valid = min(R, a.N - n0);
-      const float* tile = red + (ti & 3) * R * MP;
+      const float* tile = red + (ti & 3) * R * RP;
       cluster_wait(ti);
       const int rows_per_rank = (R + split - 1) / split;
       const int r_begin = static_cast<int>(blockIdx.y) * rows_per_rank;
@@ -687,7 +690,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
           float4 part[8];
 #pragma unroll
           for (int c = 0; c < 8; ++c)
-            part[c] = c < split ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, c) + r * MP + m)
+            part[c] = c < split ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, c) + r * RP + m)
                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
@@ -709,7 +712,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         float part[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c)   // all the remote reads in flight together
-          part[c] = c < split ? cluster.map_shared_rank(tile, c)[r * MP + m] : 0.0f;
+          part[c] = c < split ? cluster.map_shared_rank(tile, c)[r * RP + m] : 0.0f;
         float v = 0.0f;
 #pragma unroll
         for (int c = 0; c < 8; ++c) v += part[c];
@@ -721,7 +724,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       const int n0 = (static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x)) * R;
       const int rows_valid = min(R, a.N - n0);
       const float2* so_cur = so + (ti & 1) * so_buf;
-      float* red_cur = solo ? red + (ti & 1) * R * MP * (partials ? kConsumerWarps : 1) : red + (ti & 3) * R * MP;
+      float* red_cur = solo ? red + (ti & 1) * R * (partials ? kConsumerWarps * MP : RP) : red + (ti & 3) * R * RP;
       const bool has_next = ti + 1 < n_my;
       if (has_next) scale_load(n0 + static_cast<int>(gridDim.x) * R);
 
@@ -789,7 +792,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             for (int i = 0; i < 4; ++i) {
               const int row = row_base + rt * 16 + g + ((i & 2) ? 8 : 0);
               const int col = mb * 8 + 2 * t + (i & 1);
-              atomicAdd(&red_cur[row * MP + col], acc[rt][mb][i]);
+              atomicAdd(&red_cur[row * RP + col], acc[rt][mb][i]);
               acc[rt][mb][i] = 0.0f;
             }
       }
@@ -809,8 +812,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         } else {
           for (int idx = tid; idx < rows_valid * a.M; idx += kConsumerThreads) {
             const int r = idx % rows_valid, m = idx / rows_valid;
-            const float v = red_cur[r * MP + m];
-            red_cur[r * MP + m] = 0.0f;   // this buffer is added into again two tiles from now
+            const float v = red_cur[r * RP + m];
+            red_cur[r * RP + m] = 0.0f;   // this buffer is added into again two tiles from now
             store_output<FMT, GROUPED>(a, v, m, n0 + r);
           }
         }
@@ -820,8 +823,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         // Buffer (ti + 1) mod 4 held tile ti - 3.  Every peer read it before arriving for tile
         // ti - 1, which this CTA has just waited for: clear it for tile ti + 1.
         if (ti >= 3) {
-          float* next = red + ((ti + 1) & 3) * R * MP;
-          for (int i = tid; i < R * MP; i += kConsumerThreads) next[i] = 0.0f;
+          float* next = red + ((ti + 1) & 3) * R * RP;
+          for (int i = tid; i < R * RP; i += kConsumerThreads) next[i] = 0.0f;
         }
         consumer_barrier();
       }
@@ -854,7 +857,7 @@ int ChunkK(int fmt, int mb, int rt) { return ChunkRowBytes(mb, rt) * 8 / BitsOf(
 size_t SmemFor(const Plan& pl, int M, int k_per_cta) {
   const int R = 16 * pl.rt, MP = 8 * pl.mb, groups = k_per_cta / kGroupK;
   size_t off = (static_cast<size_t>(2 * pl.stages) * 8 + 127) & ~static_cast<size_t>(127);
-  off += static_cast<size_t>(pl.mb == 1 ? 2 * kConsumerWarps : 4) * R * MP * 4;
+  off += static_cast<size_t>(pl.mb == 1 ? 2 * kConsumerWarps * MP : 4 * (MP + 4)) * R * 4;
   off += (static_cast<size_t>(groups) * MP * 4 + 127) & ~static_cast<size_t>(127);
   off += (static_cast<size_t>(groups) * M * 128 + 127) & ~static_cast<size_t>(127);
   if (pl.grouped) off += (static_cast<size_t>(2) * groups * R * 8 + 127) & ~static_cast<size_t>(127);
@@ -911,6 +914,7 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
   // Up to 8 rows of x: two 16-row tiles per step (two independent dequant/MMA chains per
   // warp) when 32-row tiles still give every SM one; only on the unrolled K = 4096 path.
   if (pl.mb == 1 && K == 64 * kGroupK && CeilDiv(N, 32) >= sm_count && !no_tall_tiles) pl.rt = 2;
+  if (pl.mb == 4 && no_tall_tiles) pl.rt = 2;   // the 64-row tile's buffers did not fit beside this slice of x
   pl.tiles = static_cast<int>(CeilDiv(N, 16 * pl.rt));
   // K is split across a cluster only when the row tiles alone cannot occupy the
   // GPU, or when a CTA's slice of x would not fit shared memory.
@@ -941,7 +945,7 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
     if (pl.rt > pl.mb) break;   // the two-tile variant exists for the whole K = 4096 only
   }
   if (!found) {
-    if (pl.mb == 1 && pl.rt == 2 && !no_tall_tiles) return MakePlanImpl(p, sm_count, max_smem, out, true);
+    if (((pl.mb == 1 && pl.rt == 2) || pl.mb == 4) && !no_tall_tiles) return MakePlanImpl(p, sm_count, max_smem, out, true);
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: M=%d K=%d does not fit shared memory (limit %d bytes)", M, K, max_smem);
   }
   *out = pl;
@@ -1004,6 +1008,7 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
       if (args.k_per_cta != 64 * kGroupK) return cudaErrorInvalidValue;
       return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
+    case 42: return LaunchOne<FMT, 4, 2, GROUPED, 0>(pl, args, grid, stream);
     case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
   }
   return cudaErrorInvalidValue;
