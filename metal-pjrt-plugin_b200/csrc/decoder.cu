@@ -60,6 +60,20 @@ __global__ void residual_rmsnorm_kernel(__nv_bfloat16* x, const float* y, const 
     h[base + i] = __float2bfloat16_rn((row[i] * r) * __bfloat162float(gain[i]));
 }
 
+// bf16 -> f32, eight elements per thread (count a multiple of 8, 16-byte aligned buffers).
+__global__ void widen_bf16_kernel(const __nv_bfloat16* in, float* out, int64_t count) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= count) return;
+  const uint4 raw = *reinterpret_cast<const uint4*>(in + i);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  float4 lo = make_float4(bf16_lo(w[0]), bf16_hi(w[0]), bf16_lo(w[1]), bf16_hi(w[1]));
+  float4 hi = make_float4(bf16_lo(w[2]), bf16_hi(w[2]), bf16_lo(w[3]), bf16_hi(w[3]));
+  *reinterpret_cast<float4*>(out + i) = lo;
+  *reinterpret_cast<float4*>(out + i + 4) = hi;
+}
+
 }  // namespace
 
 struct b200_decoder {
@@ -73,6 +87,7 @@ struct b200_decoder {
   // activations (device, sized for max_batch)
   __nv_bfloat16 *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr;
   float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr, *inv_freq = nullptr;
+  __nv_bfloat16* logits_bf16 = nullptr;   // LM head output of the tensor-core route (batches above 8)
   bool use_graph = true;
   cudaStream_t capture_stream = nullptr;  // graphs are captured here (the caller's stream may be the legacy one)
   std::map<std::tuple<int, const void*, const void*, const void*>, cudaGraphExec_t> graphs;
@@ -189,21 +204,55 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
     }
   }
   // LM head: bf16 rows, logits are the bf16-rounded products widened to f32 (qwen3.py:389-390)
-  b200_qmm_params p = {};
-  p.bits = 16;
-  p.epilogue = B200_QMM_OUT_F32;
-  p.x = fuse_norm ? d->x : d->h;
-  if (fuse_norm) {
-    p.prologue = B200_QMM_PRO_RMSNORM;
-    p.prologue_gain = d->final_norm;
-    p.eps = c.rms_eps;
+  float* head_out = tp ? d->logits_local : logits;
+  const int64_t head_count = static_cast<int64_t>(batch) * c.vocab;
+  if (batch > 8 && d->logits_bf16 != nullptr && head_count % 8 == 0 && Aligned(head_out, 16)) {
+    // above 8 rows x no longer fits beside a streaming CTA's ring without splitting K; the
+    // tensor-core GEMM (x . W^T, bf16 out) plus a widening pass is several times faster
+    b200_gemm_params g = {};
+    g.m = batch;
+    g.n = c.vocab;
+    g.k = E;
+    g.batch = 1;
+    g.alpha = 1.0;
+    g.a.ptr = d->h;
+    g.a.ld = E;
+    g.a.dtype = B200_BF16;
+    g.b.ptr = const_cast<void*>(d->lm_head);
+    g.b.ld = E;
+    g.b.dtype = B200_BF16;
+    g.b.transpose = 1;
+    g.c.ptr = d->logits_bf16;
+    g.c.ld = c.vocab;
+    g.c.dtype = B200_BF16;
+    b200_epilogue epi = {};
+    B200_TRY(b200_gemm(ctx, stream, &g, &epi));
+    B200_TRY(BeginLaunch(ctx));
+    LaunchCfg lc;
+    lc.stream = stream;
+    lc.pdl = true;
+    lc.block = dim3(256);
+    lc.grid = dim3(static_cast<unsigned>(CeilDiv(head_count / 8, 256)));
+    cudaError_t e = Launch(lc, widen_bf16_kernel, static_cast<const __nv_bfloat16*>(d->logits_bf16), head_out, head_count);
+    if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "widen launch: %s", cudaGetErrorString(e)));
+    B200_TRY(EndLaunch(ctx, "widen"));
+  } else {
+    b200_qmm_params p = {};
+    p.bits = 16;
+    p.epilogue = B200_QMM_OUT_F32;
+    p.x = fuse_norm ? d->x : d->h;
+    if (fuse_norm) {
+      p.prologue = B200_QMM_PRO_RMSNORM;
+      p.prologue_gain = d->final_norm;
+      p.eps = c.rms_eps;
+    }
+    p.q = d->lm_head;
+    p.out = head_out;
+    p.M = batch;
+    p.N = c.vocab;
+    p.K = E;
+    B200_TRY(b200_qmm_run(ctx, stream, &p));
   }
-  p.q = d->lm_head;
-  p.out = tp ? d->logits_local : logits;
-  p.M = batch;
-  p.N = c.vocab;
-  p.K = E;
-  B200_TRY(b200_qmm_run(ctx, stream, &p));
   if (tp) B200_TRY(TpAllGather(d->tp, stream, d->logits_local, logits, static_cast<int64_t>(batch) * c.vocab, B200_F32));
   return B200_OK;
 }
@@ -254,6 +303,7 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
     e = cudaMalloc(reinterpret_cast<void**>(&d->attn_scratch),
                    b200_attention_scratch_bytes(c.max_batch, c.heads, c.head_dim, c.max_len));
   if (e == cudaSuccess && tp != nullptr && tp->world > 1) e = Alloc(&d->logits_local, B * c.vocab);
+  if (e == cudaSuccess && c.max_batch > 8) e = Alloc(&d->logits_bf16, B * c.vocab);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = Alloc(&d->inv_freq, static_cast<size_t>(c.head_dim / 2));
   if (e == cudaSuccess) {
@@ -279,7 +329,8 @@ void b200_decoder_destroy(b200_decoder* d) {
   for (void* p : {static_cast<void*>(d->x), static_cast<void*>(d->h), static_cast<void*>(d->qkv),
                   static_cast<void*>(d->attn), static_cast<void*>(d->gu),
                   static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
-                  static_cast<void*>(d->logits_local), static_cast<void*>(d->inv_freq)})
+                  static_cast<void*>(d->logits_local), static_cast<void*>(d->inv_freq),
+                  static_cast<void*>(d->logits_bf16)})
     if (p != nullptr) cudaFree(p);
   delete d;
 }
