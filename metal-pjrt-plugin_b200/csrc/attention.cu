@@ -235,10 +235,13 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
         const uint32_t w[4] = {vreg[j].x, vreg[j].y, vreg[j].z, vreg[j].w};
         float v[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int s = 8 * j + e;
-          v[e] = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
-          if (s0 + s >= n_old) v[e] = (owner && s0 + s == pos) ? vnew[tid] : 0.0f;
+        for (int e = 0; e < 8; ++e) v[e] = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+        if (s0 + 8 * j + 8 > n_old) {   // only the chunk that holds the newest position has such slots
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int s = 8 * j + e;
+            if (s0 + s >= n_old) v[e] = (owner && s0 + s == pos) ? vnew[tid] : 0.0f;
+          }
         }
         // the eight probabilities of a head as two 16-byte broadcast reads (the loop is bound by
         // shared-memory instructions otherwise: one scalar read per multiply-add)

@@ -260,7 +260,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int split = gridDim.y;   // CTAs of one cluster along K; every CTA walks tiles blockIdx.x, + gridDim.x, ...
-  const bool solo = split == 1;
+  // The unrolled variants (KG > 0) are only launched without a K split, so they carry none of
+  // the cluster code (and none of its registers).
+  const bool solo = KG > 0 || split == 1;
   const int k_begin = blockIdx.y * a.k_per_cta;
   const int groups_cta = a.k_per_cta / kGroupK;
   const int n_chunks = (a.k_per_cta + kChunkK - 1) / kChunkK;
@@ -683,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       cg::cluster_group cluster = cg::this_cluster();
       // adjacent threads read adjacent words of the peers' tiles ([row][batch], batch fastest);
       // four batch columns per thread and read when the batch allows it
-      if (a.M % 4 == 0) {
+      if (a.M % 4 == 0 && a.M >= 16) {   // below 16 rows too few (row, 4-column) items to hide the latency
         const int mq = a.M / 4;
         for (int idx = tid; idx < r_count * mq; idx += kConsumerThreads) {
           const int r = r_begin + idx / mq, m = (idx % mq) * 4;
@@ -1002,10 +1004,10 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
   switch (pl.mb * 10 + pl.rt) {
     case 11:
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
-      if (args.k_per_cta == 64 * kGroupK) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
+      if (args.k_per_cta == 64 * kGroupK && pl.split == 1) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
     case 12:
-      if (args.k_per_cta != 64 * kGroupK) return cudaErrorInvalidValue;
+      if (args.k_per_cta != 64 * kGroupK || pl.split != 1) return cudaErrorInvalidValue;
       return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
     case 42: return LaunchOne<FMT, 4, 2, GROUPED, 0>(pl, args, grid, stream);
