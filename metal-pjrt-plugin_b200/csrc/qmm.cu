@@ -200,7 +200,7 @@ __device__ __forceinline__ void consumer_barrier() {
 template <int FMT, bool GROUPED>
 __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, int n) {
   if (!GROUPED && Fmt<FMT>::kBits != 16) v *= ldg_bf16(a.scale + n);
-  if (a.epilogue == kEpilogueGemm) {
+  if (FMT == kBf16 && a.epilogue == kEpilogueGemm) {   // b200_gemm's few-row route: 16-bit weights only
     const size_t o = static_cast<size_t>(m) * a.out_vec_stride + static_cast<size_t>(n) * a.out_row_stride;
     v *= a.alpha;
     const int bi = a.bias_by_vec ? m : n;
