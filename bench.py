@@ -270,6 +270,9 @@ def run_ours(args):
     torch.cuda.set_device(local)
     device = f"cuda:{local}"
     if world > 1:
+        # the only NCCL traffic is the 0.6 MB all-gather of logits: in-switch reduction buys nothing,
+        # and without it no rank's memory is bound to an NVLink multicast object
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(device))
     ctx = pkg.default_context(local)
     tp = None
