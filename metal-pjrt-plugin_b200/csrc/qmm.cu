@@ -915,7 +915,11 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
   pl.rt = pl.mb;
   // Up to 8 rows of x: two 16-row tiles per step (two independent dequant/MMA chains per
   // warp) when 32-row tiles still give every SM one; only on the unrolled K = 4096 path.
-  if (pl.mb == 1 && K == 64 * kGroupK && CeilDiv(N, 32) >= sm_count && !no_tall_tiles) pl.rt = 2;
+  // ... or, up to 2 rows of x, when they cost the busiest SM no more rows than 16-row tiles would (N = 4096 on 148 SMs:
+  // one 32-row tile each for 128 CTAs against two 16-row tiles for 108 of 148).
+  const int64_t rows_tall = CeilDiv(CeilDiv(N, 32), sm_count) * 32, rows_short = CeilDiv(CeilDiv(N, 16), sm_count) * 16;
+  if (pl.mb == 1 && K == 64 * kGroupK && (CeilDiv(N, 32) >= sm_count || (M <= 2 && rows_tall <= rows_short)) && !no_tall_tiles)
+    pl.rt = 2;
   if (pl.mb == 4 && no_tall_tiles) pl.rt = 2;   // the 64-row tile's buffers did not fit beside this slice of x
   pl.tiles = static_cast<int>(CeilDiv(N, 16 * pl.rt));
   // K is split across a cluster only when the row tiles alone cannot occupy the
@@ -931,7 +935,8 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
     const int kc = K / split;
     const bool fills = static_cast<int64_t>(pl.tiles) * split >= sm_count;
     const bool last = split == 8 || K % (2 * split * kGroupK) != 0;
-    if (static_cast<size_t>(M) * kc * 2 > x_budget || !(fills || last)) continue;
+    const bool tall = pl.rt > pl.mb;   // the two-tile variant never splits K
+    if (static_cast<size_t>(M) * kc * 2 > x_budget || !(fills || last || tall)) continue;
     pl.split = split;
     const int chunks = static_cast<int>(CeilDiv(kc, ChunkK(pl.fmt, pl.mb, pl.rt)));
     pl.grid_x = std::min(pl.tiles, std::max(1, sm_count / split));
