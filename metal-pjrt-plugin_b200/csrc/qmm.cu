@@ -263,6 +263,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   // The unrolled variants (KG > 0) are only launched without a K split, so they carry none of
   // the cluster code (and none of its registers).
   const bool solo = KG > 0 || split == 1;
+  // ... and are only launched with 16-byte-loadable x / scales and without the silu prologue.
+  const bool x_vec = KG > 0 || a.x_vec != 0;
+  const bool scale_vec = KG > 0 || a.scale_vec != 0;
   const int k_begin = blockIdx.y * a.k_per_cta;
   const int groups_cta = a.k_per_cta / kGroupK;
   const int n_chunks = (a.k_per_cta + kChunkK - 1) / kChunkK;
@@ -346,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     const int nch = R * (groups_cta / 8);
     uint4 sreg = make_uint4(0, 0, 0, 0), breg = make_uint4(0, 0, 0, 0);
     auto scale_load = [&](int n0) {
-      if (GROUPED && a.scale_vec && tid < nch) {
+      if (GROUPED && scale_vec && tid < nch) {
         const int c = tid / R, r = tid - c * R;
         const size_t o = static_cast<size_t>(min(n0 + r, a.N - 1)) * a.scale_ld + g0 + 8 * c;
         sreg = __ldg(reinterpret_cast<const uint4*>(a.scale + o));
@@ -366,7 +369,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     };
     auto scale_store = [&](int n0, float2* dstbuf) {
       if (!GROUPED) return;
-      if (a.scale_vec) {
+      if (scale_vec) {
         if (tid < nch) put8(dstbuf, tid / R, tid % R, sreg, breg);
         for (int idx = tid + kConsumerThreads; idx < nch; idx += kConsumerThreads) {   // rarely taken
           const int c = idx / R, r = idx - c * R;
@@ -402,7 +405,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         ss[m] = 0.0f;
         if (m < a.M) {
           const __nv_bfloat16* xr = a.x + static_cast<size_t>(m) * a.ldx;
-          if (a.x_vec) {
+          if (x_vec) {
             for (int i = tid * 8; i < a.K; i += kConsumerThreads * 8) {
               const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr + i));
               const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -448,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         const int run0 = kOneRun ? 16 * ut : 8 * ut;
         const int run1 = kOneRun ? 16 * ut + 8 : 32 + 8 * ut;
         auto load_run = [&](const __nv_bfloat16* base, int k, float* dst) {
-            if (a.x_vec) {
+            if (x_vec) {
               const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + k));
               const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -493,7 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             const float rr = rinv[um];
 #pragma unroll
             for (int j = 0; j < 16; ++j) e[j] = bf16_round((e[j] * rr) * gn[j]);
-          } else if (a.prologue == B200_QMM_PRO_SILU_MUL) {
+          } else if (KG == 0 && a.prologue == B200_QMM_PRO_SILU_MUL) {
             // x is [M, 2K]: gate in the first K columns, up in the last K
             float up[16];
             load_run(xr + a.K, kbase + run0, up);
@@ -918,7 +921,12 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
   // ... or, up to 2 rows of x, when they cost the busiest SM no more rows than 16-row tiles would (N = 4096 on 148 SMs:
   // one 32-row tile each for 128 CTAs against two 16-row tiles for 108 of 148).
   const int64_t rows_tall = CeilDiv(CeilDiv(N, 32), sm_count) * 32, rows_short = CeilDiv(CeilDiv(N, 16), sm_count) * 16;
-  if (pl.mb == 1 && K == 64 * kGroupK && (CeilDiv(N, 32) >= sm_count || (M <= 2 && rows_tall <= rows_short)) && !no_tall_tiles)
+  // the unrolled variants take 16-byte loads of x, gain, scales and offsets for granted
+  const int64_t ldx = p->ldx ? p->ldx : (p->prologue == B200_QMM_PRO_SILU_MUL ? 2 * p->K : p->K);
+  const bool fast_ok = p->prologue != B200_QMM_PRO_SILU_MUL && Aligned(p->x, 16) && ldx % 8 == 0 &&
+                       (p->prologue != B200_QMM_PRO_RMSNORM || Aligned(p->prologue_gain, 16)) &&
+                       (!pl.grouped || (Aligned(p->scale, 16) && (p->bits != 4 || Aligned(p->bias, 16))));
+  if (fast_ok && pl.mb == 1 && K == 64 * kGroupK && (CeilDiv(N, 32) >= sm_count || (M <= 2 && rows_tall <= rows_short)) && !no_tall_tiles)
     pl.rt = 2;
   if (pl.mb == 4 && no_tall_tiles) pl.rt = 2;   // the 64-row tile's buffers did not fit beside this slice of x
   pl.tiles = static_cast<int>(CeilDiv(N, 16 * pl.rt));
@@ -1004,15 +1012,22 @@ cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
   return Launch(lc, kernel, args);
 }
 
+// What the unrolled (KG > 0) variants are compiled for.
+template <bool GROUPED>
+bool FastPathOk(const QmmArgs& a) {
+  return a.x_vec && (!GROUPED || a.scale_vec) && a.prologue != B200_QMM_PRO_SILU_MUL;
+}
+
 template <int FMT, bool GROUPED>
 cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
   switch (pl.mb * 10 + pl.rt) {
     case 11:
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
-      if (args.k_per_cta == 64 * kGroupK && pl.split == 1) return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
+      if (args.k_per_cta == 64 * kGroupK && pl.split == 1 && FastPathOk<GROUPED>(args))
+        return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
     case 12:
-      if (args.k_per_cta != 64 * kGroupK || pl.split != 1) return cudaErrorInvalidValue;
+      if (args.k_per_cta != 64 * kGroupK || pl.split != 1 || !FastPathOk<GROUPED>(args)) return cudaErrorInvalidValue;
       return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
     case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
     case 42: return LaunchOne<FMT, 4, 2, GROUPED, 0>(pl, args, grid, stream);

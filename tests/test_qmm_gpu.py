@@ -181,13 +181,31 @@ def test_edge_cases():
     assert p.default_context().error() == 0
 
 
-@pytest.mark.parametrize("m", [1, 3, 8])
+def test_unaligned_inputs_take_the_general_variant():
+    """K = 4096 with x (or the scales) off a 16-byte boundary: the unrolled variants assume
+    16-byte loads, so the general one must be chosen, with the same result (to bf16 rounding)."""
+    import torch
+    p = pkg()
+    x, packed, s, b, _ = inputs.config4(2, 4096, 4096)
+    w = _w4(packed, s, b)
+    ref = host(p.qwen3.linear(dev(x), w)).astype(np.float32)
+    xo = torch.zeros((2, 4096 + 8), dtype=torch.bfloat16, device="cuda")
+    xo[:, 1:4097] = dev(x)
+    assert rel_rms_err(host(p.qwen3.linear(xo[:, 1:4097], w)).astype(np.float32), ref) <= 2e-3   # x two bytes off
+    so = torch.zeros(s.size + 1, dtype=torch.bfloat16, device="cuda")
+    so[1:] = dev(s).reshape(-1)
+    w2 = dict(w, s=so[1:].reshape(s.shape))
+    assert rel_rms_err(host(p.qwen3.linear(dev(x), w2)).astype(np.float32), ref) <= 2e-3          # scales two bytes off
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 8])
 @pytest.mark.parametrize("bits", [4, 16])
-def test_fused_rmsnorm_prologue(m, bits):
+@pytest.mark.parametrize("n", [512, 4096])   # K split across a cluster (two-pass norm) / whole rows per CTA (one pass)
+def test_fused_rmsnorm_prologue(m, bits, n):
     """linear(rms_norm(x, gain, eps), w) with the norm fused into the input staging."""
     from oracle import rownorm
     p = pkg()
-    k, n = 1024, 512
+    k = 1024
     x, packed, s, b, _ = inputs.config4(m, k, n)
     gain = (1 + 0.1 * np.random.default_rng(3).standard_normal(k, dtype=np.float32)).astype(bf16)
     h = rownorm.rms_norm(x, gain, 1e-6)
