@@ -240,8 +240,11 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
 // KG > 0: the CTA's K slice is exactly KG groups (and MB == 1): every warp owns
 // a compile-time set of KG / 16 groups, keeps their x fragments in registers for
 // all row tiles, and its loop over them is fully unrolled.  KG == 0: any K.
-template <int FMT, int MB, int RT, bool GROUPED, int KG>
+// LEAN: launched only without a K split and with 16-byte-loadable x, gain, scales and offsets, so
+// none of the code for the other cases is compiled in (the unrolled variants, KG > 0, are always lean).
+template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0)>
 __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
+  static_assert(KG == 0 || LEAN, "the unrolled variants are lean");
   using F = Fmt<FMT>;
   constexpr int R = 16 * RT;
   constexpr int MP = 8 * MB;
@@ -262,10 +265,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   const int split = gridDim.y;   // CTAs of one cluster along K; every CTA walks tiles blockIdx.x, + gridDim.x, ...
   // The unrolled variants (KG > 0) are only launched without a K split, so they carry none of
   // the cluster code (and none of its registers).
-  const bool solo = KG > 0 || split == 1;
+  const bool solo = LEAN || split == 1;
   // ... and are only launched with 16-byte-loadable x / scales and without the silu prologue.
-  const bool x_vec = KG > 0 || a.x_vec != 0;
-  const bool scale_vec = KG > 0 || a.scale_vec != 0;
+  const bool x_vec = LEAN || a.x_vec != 0;
+  const bool scale_vec = LEAN || a.scale_vec != 0;
   const int k_begin = blockIdx.y * a.k_per_cta;
   const int groups_cta = a.k_per_cta / kGroupK;
   const int n_chunks = (a.k_per_cta + kChunkK - 1) / kChunkK;
@@ -971,9 +974,9 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   return MakePlanImpl(p, sm_count, max_smem, out, false);
 }
 
-template <int FMT, int MB, int RT, bool GROUPED, int KG>
+template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0)>
 cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
-  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG>;
+  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG, LEAN>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
   if (e != cudaSuccess) return e;
   LaunchCfg lc;
@@ -1025,6 +1028,9 @@ cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
       if (args.k_per_cta == 64 * kGroupK && pl.split == 1 && FastPathOk<GROUPED>(args))
         return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
+      // any K (the down projection, K = 12288, with its silu prologue): the lean build when it applies
+      if (pl.split == 1 && args.x_vec && (!GROUPED || args.scale_vec))
+        return LaunchOne<FMT, 1, 1, GROUPED, 0, true>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
     case 12:
       if (args.k_per_cta != 64 * kGroupK || pl.split != 1 || !FastPathOk<GROUPED>(args)) return cudaErrorInvalidValue;
