@@ -761,6 +761,35 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             if (lane == 0) mbar_arrive(&empty[s]);
           }
         }
+      } else if (LEAN && MB == 1 && GC % kConsumerWarps == 0) {
+        // any K, lean build: the warp's GC / 16 groups of a chunk unrolled, from 32-bit shared
+        // addresses; the x fragments come from shared memory (they do not fit registers for K = 12288)
+        constexpr int JC = GC / kConsumerWarps;
+        const uint32_t a_thr = static_cast<uint32_t>(warp * F::kGroupBytes + g * kRowStride + t * (F::kBits == 4 ? 8 : 16));
+        const uint32_t so_thr = so0 + static_cast<uint32_t>((ti & 1) * so_buf * 8 + (warp * R + g) * 8);
+        for (int c = 0; c < n_chunks; ++c) {
+          const int u = ti * n_chunks + c;
+          const int s = u % NS;
+          if (!dead && !mbar_wait_bounded(&full[s], (u / NS) & 1)) {
+            report_timeout(a.status, 200 + s);
+            dead = true;
+          }
+          const int chunk_groups = min(kChunkK, a.k_per_cta - c * kChunkK) / kGroupK;
+          const uint32_t a_chunk = stage0 + static_cast<uint32_t>(s) * kStageBytes + a_thr;
+          const uint32_t so_chunk = so_thr + static_cast<uint32_t>(c * GC * R * 8);
+#pragma unroll
+          for (int j = 0; j < JC; ++j) {
+            if (warp + kConsumerWarps * j < chunk_groups) {   // the last chunk of a K that is no multiple of the chunk
+              uint32_t xf[MB][8];
+              float xs2[MB][2];
+              load_x(c * GC + warp + kConsumerWarps * j, xf, xs2);
+              do_group32(a_chunk + static_cast<uint32_t>(kConsumerWarps * j * F::kGroupBytes),
+                         so_chunk + static_cast<uint32_t>(kConsumerWarps * j * R * 8), xf, xs2);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+        }
       } else {
         for (int c = 0; c < n_chunks; ++c) {
           const int u = ti * n_chunks + c;
