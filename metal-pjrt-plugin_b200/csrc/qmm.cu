@@ -242,9 +242,11 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
 // all row tiles, and its loop over them is fully unrolled.  KG == 0: any K.
 // LEAN: launched only without a K split and with 16-byte-loadable x, gain, scales and offsets, so
 // none of the code for the other cases is compiled in (the unrolled variants, KG > 0, are always lean).
-template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0)>
+// VEC: the 16-byte-load assumption alone, for the builds that do split K (LEAN implies it).
+template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN>
 __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   static_assert(KG == 0 || LEAN, "the unrolled variants are lean");
+  static_assert(!LEAN || VEC, "lean implies 16-byte loads");
   using F = Fmt<FMT>;
   constexpr int R = 16 * RT;
   constexpr int MP = 8 * MB;
@@ -267,8 +269,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   // the cluster code (and none of its registers).
   const bool solo = LEAN || split == 1;
   // ... and are only launched with 16-byte-loadable x / scales and without the silu prologue.
-  const bool x_vec = LEAN || a.x_vec != 0;
-  const bool scale_vec = LEAN || a.scale_vec != 0;
+  const bool x_vec = VEC || a.x_vec != 0;
+  const bool scale_vec = VEC || a.scale_vec != 0;
   const int k_begin = blockIdx.y * a.k_per_cta;
   const int groups_cta = a.k_per_cta / kGroupK;
   const int n_chunks = (a.k_per_cta + kChunkK - 1) / kChunkK;
@@ -1003,9 +1005,9 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   return MakePlanImpl(p, sm_count, max_smem, out, false);
 }
 
-template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0)>
+template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN>
 cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
-  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG, LEAN>;
+  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG, LEAN, VEC>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
   if (e != cudaSuccess) return e;
   LaunchCfg lc;
@@ -1052,21 +1054,28 @@ bool FastPathOk(const QmmArgs& a) {
 
 template <int FMT, bool GROUPED>
 cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
+  const bool vec = args.x_vec && (!GROUPED || args.scale_vec);   // 16-byte loads of x, scales and offsets
   switch (pl.mb * 10 + pl.rt) {
     case 11:
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
       if (args.k_per_cta == 64 * kGroupK && pl.split == 1 && FastPathOk<GROUPED>(args))
         return LaunchOne<FMT, 1, 1, GROUPED, 64>(pl, args, grid, stream);
       // any K (the down projection, K = 12288, with its silu prologue): the lean build when it applies
-      if (pl.split == 1 && args.x_vec && (!GROUPED || args.scale_vec))
-        return LaunchOne<FMT, 1, 1, GROUPED, 0, true>(pl, args, grid, stream);
+      if (pl.split == 1 && vec) return LaunchOne<FMT, 1, 1, GROUPED, 0, true>(pl, args, grid, stream);
+      if (vec) return LaunchOne<FMT, 1, 1, GROUPED, 0, false, true>(pl, args, grid, stream);
       return LaunchOne<FMT, 1, 1, GROUPED, 0>(pl, args, grid, stream);
     case 12:
       if (args.k_per_cta != 64 * kGroupK || pl.split != 1 || !FastPathOk<GROUPED>(args)) return cudaErrorInvalidValue;
       return LaunchOne<FMT, 1, 2, GROUPED, 64>(pl, args, grid, stream);
-    case 22: return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
-    case 42: return LaunchOne<FMT, 4, 2, GROUPED, 0>(pl, args, grid, stream);
-    case 44: return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
+    case 22:
+      if (vec) return LaunchOne<FMT, 2, 2, GROUPED, 0, false, true>(pl, args, grid, stream);
+      return LaunchOne<FMT, 2, 2, GROUPED, 0>(pl, args, grid, stream);
+    case 42:
+      if (vec) return LaunchOne<FMT, 4, 2, GROUPED, 0, false, true>(pl, args, grid, stream);
+      return LaunchOne<FMT, 4, 2, GROUPED, 0>(pl, args, grid, stream);
+    case 44:
+      if (vec) return LaunchOne<FMT, 4, 4, GROUPED, 0, false, true>(pl, args, grid, stream);
+      return LaunchOne<FMT, 4, 4, GROUPED, 0>(pl, args, grid, stream);
   }
   return cudaErrorInvalidValue;
 }
