@@ -10,9 +10,17 @@ JSON line:
             CUDA events on the launching stream, max over ranks);
   e2e       the same through the public call with pinned-host tokens copied in
             and the logits copied out every step;
-  roofline  the dominant kernel (int4 dequant-GEMV): the step's 4 x layers
-            projection launches replayed back to back over their own distinct
-            weight buffers, algorithmic bytes / mean launch time / measured HBM peak;
+  roofline  the dominant kernel.  On one GPU at small batch the whole step is ONE
+            persistent kernel (decode_stream_kernel): its algorithmic bytes (int4
+            weights + LM head + KV cache read) / its launch duration / measured HBM
+            peak.  Otherwise the int4 dequant-GEMV (qgemv_kernel): the step's 4 x
+            layers projection launches replayed back to back over their own weights;
+  ops       the stand-alone operators of the C ABI, timed after the headline (CUDA
+            events, buffers rotated beyond L2): the int4 / int8 dequant-GEMV on the
+            Qwen3-8B shapes, the bf16 GEMM sweep of configs[1], the row reductions,
+            configs[0]'s block;
+  parity    a small decoder step (sharded like the benchmarked one when N > 1)
+            against the NumPy oracle, outside the timed regions;
   cpu_baseline  the C restatement of the reference's decode math (oracle/)
             on this host's cores, on a bounded sample scaled to a full step.
 --impl reference times only that CPU restatement (the reference's own
@@ -138,6 +146,8 @@ def cpu_baseline(cfg, batch, steps=1, warmup=0, run_layers=2, run_vocab=8192):
     import ml_dtypes
     from oracle import cpu_ref
     bf16 = ml_dtypes.bfloat16
+    # every host core, whatever OMP_NUM_THREADS a launcher exported (torchrun sets it to 1)
+    cpu_ref.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     sub = dict(cfg, layers=run_layers)
     params = host_sample_params(cfg, run_layers, run_vocab)
     rng = np.random.default_rng(5)

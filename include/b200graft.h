@@ -232,18 +232,31 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
 void b200_decoder_destroy(b200_decoder* dec);
 /* tokens: device int32 [batch]; pos: device int32 [1] (position of the new token,
  * every sequence the same, qwen3.py:356); logits: device f32 [batch, vocab_total]
- * (with tp: the all-gathered logits, rank-major).  Enqueues on `stream`; the
- * first call for a batch size captures a CUDA graph, later calls replay it. */
+ * (with tp: the all-gathered logits, rank-major).  Enqueues on `stream`.
+ * On one GPU and up to a few rows the whole step is ONE persistent kernel that reads
+ * tokens / pos / logits pointers afresh at every call.  Otherwise the step is a sequence
+ * of kernels captured into a CUDA graph: tokens and pos are copied into decoder-owned
+ * buffers first, a graph is kept per (batch, logits pointer) - pass the same logits buffer
+ * every step to replay one graph - and at most 8 graphs are kept (least recently used out).
+ * Calls on one decoder are serialised by a mutex; use one decoder per host thread to overlap.
+ * The persistent kernel copies the int4 projections once, at b200_decoder_create, into its
+ * own streaming layout (a second copy of those weights in device memory; when that
+ * allocation fails the decoder silently keeps the kernel-per-operator path). */
 b200_status b200_decoder_step(b200_decoder* dec, b200_stream stream, const int32_t* tokens,
                               const int32_t* pos, float* logits, int batch);
-/* Kernels enqueued by one step at this batch size (graph nodes). */
+/* Kernels enqueued by one step at this batch size (1, or the graph's node count). */
 int64_t b200_decoder_launches_per_step(b200_decoder* dec, int batch);
+/* CUDA graphs this decoder has captured so far (0 while every step took the single kernel). */
+int64_t b200_decoder_graphs_built(b200_decoder* dec);
 
 /* Pieces of the step, exported for parity tests (bf16 throughout). */
+/* table bf16 [vocab, hidden].  A token id outside [0, vocab) reads row 0 and reports
+ * B200_INVALID_ARGUMENT through the context's device status word. */
 b200_status b200_embed(b200_context* ctx, b200_stream stream, const void* table, const int32_t* tokens,
-                       void* out, int64_t batch, int64_t hidden);
+                       void* out, int64_t batch, int64_t hidden, int64_t vocab);
 /* Per-head RMSNorm + rotate-half RoPE of q and k, and the KV-cache write at *pos
- * (qwen3.py:366-369).  qkv bf16 [B, (H + 2 KV) * D]; q_out bf16 [B, H, D]. */
+ * (qwen3.py:366-369).  qkv bf16 [B, (H + 2 KV) * D]; q_out bf16 [B, H, D].  A *pos outside
+ * [0, max_len) writes nothing and reports B200_INVALID_ARGUMENT through the status word. */
 b200_status b200_qk_norm_rope_cache(b200_context* ctx, b200_stream stream, const void* qkv,
                                     const void* q_norm, const void* k_norm, void* q_out, void* k_cache,
                                     void* v_cache, const int32_t* pos, int64_t batch, int heads,

@@ -94,7 +94,8 @@ PROTOTYPES = {
     "b200_decoder_destroy": (None, [_VP]),
     "b200_decoder_step": (_I, [_VP, _VP, _VP, _VP, _VP, _I]),
     "b200_decoder_launches_per_step": (_I64, [_VP, _I]),
-    "b200_embed": (_I, [_VP, _VP, _VP, _VP, _VP, _I64, _I64]),
+    "b200_decoder_graphs_built": (_I64, [_VP]),
+    "b200_embed": (_I, [_VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64]),
     "b200_qk_norm_rope_cache": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64,
                                      C.c_float, C.c_float]),
     "b200_attention_scratch_bytes": (C.c_size_t, [_I64, _I, _I, _I64]),

@@ -86,18 +86,21 @@ __global__ void __launch_bounds__(kThreads) attn_partial_kernel(const AttnArgs a
   __shared__ float red[G][kThreads / 32];
   __shared__ float knew[2][HALF + 4];
   __shared__ float vnew[D];
-  // The position and the cache slots of earlier steps do not come from the kernel before
-  // this one, so they are requested before waiting for it.
+  // Fused form: the position and the cache slots of earlier steps (all below *pos) do not
+  // come from the kernel before this one, so they are requested before waiting for it.
+  // Plain form: slot *pos itself is read, and the kernel before this one (the cache write
+  // of b200_qk_norm_rope_cache) may still be storing it, so the wait comes first.
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z;
+  const bool fused = a.qkv != nullptr;
+  if (!fused) pdl_wait();
   const int pos = *a.pos;
   if (pos < 0 || pos >= a.max_len) {         // nothing may be written outside the cache
     pdl_wait();
-    if (tid == 0 && a.status != nullptr) atomicCAS(a.status, 0, static_cast<int>(B200_INVALID_ARGUMENT));
+    if (tid == 0) report_status(a.status, B200_INVALID_ARGUMENT, 500);
     return;
   }
-  const bool fused = a.qkv != nullptr;
   const int n_valid = pos + 1;
   const int n_old = fused ? pos : pos + 1;   // slots whose K/V are already in the cache
   const int s0 = split * kChunk;

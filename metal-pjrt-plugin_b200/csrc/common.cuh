@@ -229,8 +229,14 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// First report wins: status[0] = code, status[1] = where (an id the reporting kernel chooses:
+// 1xx/2xx/3xx the ring and cluster waits of the streaming kernels, 4xx peer exchanges,
+// 5xx argument checks made on the device, 6xx the decode-stream kernel, 9xx the wait probe).
+__device__ __forceinline__ void report_status(int* status, int code, int where) {
+  if (status != nullptr && atomicCAS(status, 0, code) == 0) status[1] = where;
+}
 __device__ __forceinline__ void report_timeout(int* status, int where) {
-  if (status != nullptr && atomicCAS(status, 0, (int)B200_TIMEOUT) == 0) status[1] = where;
+  report_status(status, (int)B200_TIMEOUT, where);
 }
 
 // mma.sync m16n8k16, bf16 inputs, f32 accumulate (the few-row streaming path:

@@ -137,8 +137,14 @@ b200_status b200_context_error(b200_context* ctx) {
     if (e != cudaSuccess) {
       Stick(ctx, Fail(B200_INTERNAL, "reading the device status word: %s", cudaGetErrorString(e)));
     } else if (word[0] != 0) {
-      Stick(ctx, Fail(static_cast<b200_status>(word[0]),
-                      "a kernel reported status %d (bounded wait %d gave up)", word[0], word[1]));
+      if (word[0] == B200_TIMEOUT)
+        Stick(ctx, Fail(B200_TIMEOUT, "a kernel reported B200_TIMEOUT: bounded wait %d gave up", word[1]));
+      else if (word[0] == B200_INVALID_ARGUMENT)
+        Stick(ctx, Fail(B200_INVALID_ARGUMENT,
+                        "a kernel reported B200_INVALID_ARGUMENT: device-side argument check %d failed (a position "
+                        "outside the cache or a token id outside the vocabulary)", word[1]));
+      else
+        Stick(ctx, Fail(static_cast<b200_status>(word[0]), "a kernel reported status %d (site %d)", word[0], word[1]));
     }
     sticky = ctx->sticky.load();
   }

@@ -1,8 +1,11 @@
 // One decode step of the Qwen3-shaped int4 decoder
-// (examples/llm/qwen3.py:334-390 with T = 1), as a fixed sequence of this
-// library's kernels on one stream, captured once per batch size into a CUDA
-// graph (the launches carry programmatic-dependent-launch edges, so each
-// projection's weight stream starts while the kernel before it drains).
+// (examples/llm/qwen3.py:334-390 with T = 1).  Two implementations:
+//   * one persistent kernel for the whole step (decode_stream.cu) where the
+//     shapes and the batch allow it (one GPU, a few rows);
+//   * otherwise a fixed sequence of this library's kernels on one stream,
+//     captured once per batch size into a CUDA graph (the launches carry
+//     programmatic-dependent-launch edges, so each projection's weight stream
+//     starts while the kernel before it drains).
 //
 // With a tensor-parallel group the projections are sharded Megatron-style:
 // qkv and gate_up by output rows (heads / intermediate columns stay local, as
@@ -12,11 +15,13 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <list>
 #include <map>
+#include <mutex>
 #include <tuple>
 #include <vector>
 
-#include "tp.cuh"
+#include "decode_stream.cuh"
 
 using namespace b200;
 
@@ -90,8 +95,17 @@ struct b200_decoder {
   __nv_bfloat16* logits_bf16 = nullptr;   // LM head output of the tensor-core route (batches above 8)
   bool use_graph = true;
   cudaStream_t capture_stream = nullptr;  // graphs are captured here (the caller's stream may be the legacy one)
-  std::map<std::tuple<int, const void*, const void*, const void*>, cudaGraphExec_t> graphs;
+  // Captured steps, keyed by (batch, logits pointer) and most recently used first.  Tokens and
+  // the position are copied into decoder-owned buffers before every replay, so only the
+  // output pointer is baked into a graph; at most kMaxGraphs are kept (the oldest is destroyed).
+  static constexpr size_t kMaxGraphs = 8;
+  std::list<std::pair<std::pair<int, const void*>, cudaGraphExec_t>> graphs;
+  int64_t graphs_built = 0;
+  int32_t* tokens_buf = nullptr;   // int32 [max_batch]
+  int32_t* pos_buf = nullptr;      // int32 [1]
   std::map<int, int64_t> launches;
+  std::mutex mu;                   // steps may come from several host threads
+  DecodeStream* stream_path = nullptr;   // the single-kernel step, or null
 };
 
 namespace {
@@ -153,7 +167,8 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   // Up to 8 rows the RMSNorm in front of a projection is fused into its input
   // staging (h is never written); beyond that it is its own kernel.
   const bool fuse_norm = batch <= 8 && !tp;
-  B200_TRY(b200_embed(ctx, stream, d->embed, tokens, d->x, batch, E));
+  B200_TRY(b200_embed(ctx, stream, d->embed, tokens, d->x, batch, E,
+                      static_cast<int64_t>(c.vocab) * (d->tp != nullptr ? d->tp->world : 1)));
   if (!fuse_norm)
     B200_TRY(b200_rownorm(ctx, stream, 0, d->x, d->layers[0].attn_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
   for (int li = 0; li < c.layers; ++li) {
@@ -306,6 +321,8 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
   if (e == cudaSuccess && c.max_batch > 8) e = Alloc(&d->logits_bf16, B * c.vocab);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = Alloc(&d->inv_freq, static_cast<size_t>(c.head_dim / 2));
+  if (e == cudaSuccess) e = Alloc(&d->tokens_buf, B);
+  if (e == cudaSuccess) e = Alloc(&d->pos_buf, 1);
   if (e == cudaSuccess) {
     std::vector<float> f(c.head_dim / 2);
     for (int i = 0; i < c.head_dim / 2; ++i)
@@ -317,6 +334,15 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
     b200_decoder_destroy(d);
     return s;
   }
+  // B200_DECODER_NO_STREAM=1 keeps the kernel-per-operator path (an A/B switch)
+  if (!EnvFlag("B200_DECODER_NO_STREAM")) {
+    s = DecodeStreamCreate(ctx, c, d->layers, embed, final_norm, lm_head,
+                           static_cast<int64_t>(c.vocab) * (tp != nullptr ? tp->world : 1), tp, &d->stream_path);
+    if (s != B200_OK) {
+      b200_decoder_destroy(d);
+      return s;
+    }
+  }
   *out = d;
   return B200_OK;
 }
@@ -324,13 +350,15 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
 void b200_decoder_destroy(b200_decoder* d) {
   if (d == nullptr) return;
   cudaSetDevice(d->ctx->device);
+  DecodeStreamDestroy(d->stream_path);
   for (auto& kv : d->graphs) cudaGraphExecDestroy(kv.second);
   if (d->capture_stream != nullptr) cudaStreamDestroy(d->capture_stream);
   for (void* p : {static_cast<void*>(d->x), static_cast<void*>(d->h), static_cast<void*>(d->qkv),
                   static_cast<void*>(d->attn), static_cast<void*>(d->gu),
                   static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
                   static_cast<void*>(d->logits_local), static_cast<void*>(d->inv_freq),
-                  static_cast<void*>(d->logits_bf16)})
+                  static_cast<void*>(d->logits_bf16), static_cast<void*>(d->tokens_buf),
+                  static_cast<void*>(d->pos_buf)})
     if (p != nullptr) cudaFree(p);
   delete d;
 }
@@ -345,21 +373,32 @@ b200_status b200_decoder_step(b200_decoder* d, b200_stream stream, const int32_t
   if (batch == 0) return B200_OK;
   if (tokens == nullptr || pos == nullptr || logits == nullptr)
     return Fail(B200_INVALID_ARGUMENT, "b200_decoder_step: null buffer");
+  std::lock_guard<std::mutex> lock(d->mu);
+  if (DecodeStreamSupports(d->stream_path, batch)) {
+    d->launches[batch] = 1;
+    return DecodeStreamStep(d->stream_path, stream, tokens, pos, logits, nullptr, batch);
+  }
   if (!d->use_graph) {
     const int64_t before = d->ctx->launches.load();
     s = Enqueue(d, stream, tokens, pos, logits, batch);
     d->launches[batch] = d->ctx->launches.load() - before;
     return s;
   }
-  const auto key = std::make_tuple(batch, static_cast<const void*>(tokens), static_cast<const void*>(pos),
-                                   static_cast<const void*>(logits));
-  auto it = d->graphs.find(key);
+  // The graph reads tokens and the position from the decoder's own buffers, so a caller may
+  // pass fresh tensors every step without a new capture.
+  cudaError_t e = cudaMemcpyAsync(d->tokens_buf, tokens, static_cast<size_t>(batch) * sizeof(int32_t),
+                                  cudaMemcpyDeviceToDevice, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d->pos_buf, pos, sizeof(int32_t), cudaMemcpyDeviceToDevice, stream);
+  if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "staging tokens: %s", cudaGetErrorString(e)));
+  const auto key = std::make_pair(batch, static_cast<const void*>(logits));
+  auto it = d->graphs.begin();
+  while (it != d->graphs.end() && it->first != key) ++it;
   if (it == d->graphs.end()) {
     cudaStream_t cs = d->capture_stream;
-    cudaError_t e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
+    e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
     if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaStreamBeginCapture: %s", cudaGetErrorString(e)));
     const int64_t before = d->ctx->launches.load();
-    s = Enqueue(d, cs, tokens, pos, logits, batch);
+    s = Enqueue(d, cs, d->tokens_buf, d->pos_buf, logits, batch);
     const int64_t count = d->ctx->launches.load() - before;
     cudaGraph_t graph = nullptr;
     e = cudaStreamEndCapture(cs, &graph);
@@ -374,12 +413,30 @@ b200_status b200_decoder_step(b200_decoder* d, b200_stream stream, const int32_t
     if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaGraphInstantiate: %s", cudaGetErrorString(e)));
     d->ctx->launches.fetch_sub(count);  // capture enqueued nothing; replays are counted below
     d->launches[batch] = count;
-    it = d->graphs.emplace(key, exec).first;
+    ++d->graphs_built;
+    if (d->graphs.size() >= b200_decoder::kMaxGraphs) {
+      // The oldest graph may still be running on the caller's stream: wait before destroying it.
+      // This only happens to callers that rotate through more than kMaxGraphs output buffers.
+      cudaStreamSynchronize(stream);
+      cudaGraphExecDestroy(d->graphs.back().second);
+      d->graphs.pop_back();
+    }
+    d->graphs.emplace_front(key, exec);
+    it = d->graphs.begin();
+  } else if (it != d->graphs.begin()) {
+    d->graphs.splice(d->graphs.begin(), d->graphs, it);   // most recently used first
+    it = d->graphs.begin();
   }
-  cudaError_t e = cudaGraphLaunch(it->second, stream);
+  e = cudaGraphLaunch(it->second, stream);
   if (e != cudaSuccess) return Stick(d->ctx, Fail(B200_INTERNAL, "cudaGraphLaunch: %s", cudaGetErrorString(e)));
   d->ctx->launches.fetch_add(d->launches[batch]);
   return B200_OK;
+}
+
+int64_t b200_decoder_graphs_built(b200_decoder* d) {
+  if (d == nullptr) return 0;
+  std::lock_guard<std::mutex> lock(d->mu);
+  return d->graphs_built;
 }
 
 int64_t b200_decoder_launches_per_step(b200_decoder* d, int batch) {

@@ -10,10 +10,17 @@ using namespace b200;
 namespace {
 
 // ---------------------------------------------------------------------------
-__global__ void embed_kernel(const uint4* table, const int32_t* tokens, uint4* out, int vec_per_row) {
+// A token id outside [0, vocab) reads row 0 instead of memory outside the table and reports
+// B200_INVALID_ARGUMENT through the status word.
+__global__ void embed_kernel(const uint4* table, const int32_t* tokens, uint4* out, int vec_per_row, int64_t vocab,
+                             int* status) {
   pdl_wait();
   pdl_launch_dependents();
-  const int64_t row = tokens[blockIdx.x];
+  int64_t row = tokens[blockIdx.x];
+  if (row < 0 || row >= vocab) {
+    if (threadIdx.x == 0) report_status(status, B200_INVALID_ARGUMENT, 501);
+    row = 0;
+  }
   for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x)
     out[static_cast<int64_t>(blockIdx.x) * vec_per_row + i] = __ldg(table + row * vec_per_row + i);
 }
@@ -31,6 +38,7 @@ struct QkArgs {
   int heads, kv_heads, head_dim;
   int64_t max_len;
   float theta, eps;
+  int* status;
 };
 
 template <int D>
@@ -44,6 +52,10 @@ __global__ void qk_norm_rope_cache_kernel(const QkArgs a) {
   if (head >= total_heads) return;
   const int b = blockIdx.y;
   const int pos = *a.pos;
+  if (pos < 0 || pos >= a.max_len) {   // nothing may be written outside the cache
+    if (lane == 0) report_status(a.status, B200_INVALID_ARGUMENT, 502);
+    return;
+  }
   const __nv_bfloat16* src = a.qkv + (static_cast<int64_t>(b) * total_heads + head) * D;
 
   if (head >= a.heads + a.kv_heads) {  // value head: transposed cache write, V[b, kv, d, pos]
@@ -105,10 +117,10 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* gate_up, __nv_bfloat16* out
 extern "C" {
 
 b200_status b200_embed(b200_context* ctx, b200_stream stream, const void* table, const int32_t* tokens, void* out,
-                       int64_t batch, int64_t hidden) {
+                       int64_t batch, int64_t hidden, int64_t vocab) {
   b200_status s = BeginLaunch(ctx);
   if (s != B200_OK) return s;
-  if (batch < 0 || hidden < 0) return Fail(B200_INVALID_ARGUMENT, "b200_embed: negative size");
+  if (batch < 0 || hidden < 0 || vocab < 1) return Fail(B200_INVALID_ARGUMENT, "b200_embed: bad sizes");
   if (batch == 0 || hidden == 0) return B200_OK;
   if (table == nullptr || tokens == nullptr || out == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_embed: null buffer");
   if (hidden % 8 != 0 || !Aligned(table, 16) || !Aligned(out, 16))
@@ -119,7 +131,7 @@ b200_status b200_embed(b200_context* ctx, b200_stream stream, const void* table,
   lc.grid = dim3(static_cast<unsigned>(batch));
   lc.block = dim3(128);
   cudaError_t e = Launch(lc, embed_kernel, static_cast<const uint4*>(table), tokens, static_cast<uint4*>(out),
-                         static_cast<int>(hidden / 8));
+                         static_cast<int>(hidden / 8), vocab, ctx->dev_status);
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "b200_embed launch: %s", cudaGetErrorString(e)));
   return EndLaunch(ctx, "b200_embed");
 }
@@ -151,6 +163,7 @@ b200_status b200_qk_norm_rope_cache(b200_context* ctx, b200_stream stream, const
   a.max_len = max_len;
   a.theta = theta;
   a.eps = eps;
+  a.status = ctx->dev_status;
   const int total = heads + 2 * kv_heads;
   LaunchCfg lc;
   lc.stream = stream;

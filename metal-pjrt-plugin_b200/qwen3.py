@@ -174,7 +174,12 @@ class Decoder:
         return logits
 
     def launches_per_step(self, batch):
+        """1 where the whole step is the single persistent kernel, else the graph's kernel count."""
         return _lib.lib().b200_decoder_launches_per_step(self.handle, batch)
+
+    def graphs_built(self):
+        """CUDA graphs captured so far (0 while every step took the single kernel)."""
+        return _lib.lib().b200_decoder_graphs_built(self.handle)
 
     def close(self):
         if self.handle:

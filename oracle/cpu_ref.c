@@ -47,6 +47,16 @@ int oracle_threads(void) {
 #endif
 }
 
+/* Threads for the parallel loops from now on (a launcher may have exported
+ * OMP_NUM_THREADS=1; the benchmark's CPU arm asks for every core instead). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* out[m*N + n] (f32, unrounded) = sum_k x[m,k] * (q*s + b)[n,k];  M <= 32 */
 void oracle_qmv_int4(const uint16_t* x, const uint32_t* q, const uint16_t* s, const uint16_t* b, float* out,
                      int M, int N, int K) {

@@ -50,6 +50,11 @@ def threads():
     return lib().oracle_threads()
 
 
+def set_threads(n):
+    """Use n threads from now on, whatever OMP_NUM_THREADS said at load time."""
+    lib().oracle_set_threads(int(n))
+
+
 def qmv_int4(x, q, s, b):
     """x bf16 [M,K]; q uint32 [N,K/8]; s,b bf16 [N,K/64] -> f32 [M,N] (unrounded)."""
     M, K = x.shape

@@ -78,6 +78,46 @@ def test_pieces_against_oracle(B, H, KV, D, S, pos):
     assert rel_rms_err(host(out).astype(np.float32), a_ref.reshape(B, H, D).astype(np.float32)) <= 2e-2
 
 
+def test_cache_write_then_attention_back_to_back():
+    """b200_qk_norm_rope_cache followed by b200_attention_decode with no host sync in between,
+    many times: attention must see the K / V row the kernel before it has just written (the
+    two launches overlap under programmatic dependent launch)."""
+    import torch
+    from oracle.rownorm import rms_norm
+    p = pkg()
+    L = p.lib()
+    B, H, KV, D, S, pos = 2, 8, 2, 128, 192, 130
+    rng = np.random.default_rng(31)
+    qn = (1 + 0.1 * rng.standard_normal(D, dtype=np.float32)).astype(bf16)
+    kn = (1 + 0.1 * rng.standard_normal(D, dtype=np.float32)).astype(bf16)
+    kc = rng.standard_normal((B, KV, S, D), dtype=np.float32).astype(bf16)
+    vc = rng.standard_normal((B, KV, D, S), dtype=np.float32).astype(bf16)
+    rounds = 12
+    qkvs = [(3.0 * rng.standard_normal((B, (H + 2 * KV) * D), dtype=np.float32)).astype(bf16) for _ in range(rounds)]
+    kd, vd, qnd, knd = dev(kc), dev(vc), dev(qn), dev(kn)
+    qkvd = [dev(q) for q in qkvs]
+    qo = [torch.empty((B, H, D), dtype=torch.bfloat16, device="cuda") for _ in range(rounds)]
+    outs = [torch.empty((B, H, D), dtype=torch.bfloat16, device="cuda") for _ in range(rounds)]
+    posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    scratch = torch.empty(L.b200_attention_scratch_bytes(B, H, D, S) // 4, device="cuda")
+    torch.cuda.synchronize()
+    for i in range(rounds):
+        _call(p, L.b200_qk_norm_rope_cache, qkvd[i].data_ptr(), qnd.data_ptr(), knd.data_ptr(), qo[i].data_ptr(),
+              kd.data_ptr(), vd.data_ptr(), posd.data_ptr(), B, H, KV, D, S, 1e6, 1e-6)
+        _call(p, L.b200_attention_decode, qo[i].data_ptr(), kd.data_ptr(), vd.data_ptr(), outs[i].data_ptr(),
+              posd.data_ptr(), scratch.data_ptr(), B, H, KV, D, S)
+    torch.cuda.synchronize()
+    positions = np.full((B,), pos)
+    for i in range(rounds):
+        qkv = qkvs[i]
+        k_ref = odec.rope(rms_norm(qkv[:, H * D:(H + KV) * D].reshape(B, KV, D), kn, 1e-6), positions, 1e6)
+        kc2, vc2 = kc.copy(), vc.copy()
+        kc2[:, :, pos] = k_ref
+        vc2[:, :, :, pos] = qkv[:, (H + KV) * D:].reshape(B, KV, D)
+        a_ref = odec.attention_decode(host(qo[i]).reshape(B, KV, H // KV, D), kc2, vc2, pos + 1, D ** -0.5)
+        assert rel_rms_err(host(outs[i]).astype(np.float32), a_ref.reshape(B, H, D).astype(np.float32)) <= 2e-2, i
+
+
 @pytest.mark.parametrize("B,H,KV,D,S,pos", [(2, 4, 2, 64, 48, 30), (3, 8, 2, 128, 300, 299), (1, 32, 8, 128, 2176, 2048),
                                             (2, 4, 4, 128, 130, 0), (2, 8, 1, 128, 256, 64), (1, 2, 2, 64, 72, 63)])
 def test_fused_attention_step(B, H, KV, D, S, pos):
@@ -157,8 +197,19 @@ def test_silu_mul_and_embed():
     tok = np.array([3, 99, 0, 3], np.int32)
     e = torch.empty((4, 256), dtype=torch.bfloat16, device="cuda")
     tabled, tokd = dev(table), dev(tok)
-    _call(p, L.b200_embed, tabled.data_ptr(), tokd.data_ptr(), e.data_ptr(), 4, 256)
+    _call(p, L.b200_embed, tabled.data_ptr(), tokd.data_ptr(), e.data_ptr(), 4, 256, 100)
     assert np.array_equal(host(e).view(np.uint16), table[tok].view(np.uint16))
+
+
+@pytest.fixture(params=["stream", "per_op"])
+def step_path(request, monkeypatch):
+    """Both implementations of the step: the single persistent kernel (taken where the
+    shapes and the batch allow it) and the kernel-per-operator graph."""
+    if request.param == "per_op":
+        monkeypatch.setenv("B200_DECODER_NO_STREAM", "1")
+    else:
+        monkeypatch.delenv("B200_DECODER_NO_STREAM", raising=False)
+    return request.param
 
 
 def _run_decoder(cfg, batch, ctx, max_len, steps=1):
@@ -186,20 +237,57 @@ def _run_decoder(cfg, batch, ctx, max_len, steps=1):
     return results, dcache, ocache, dec
 
 
-@pytest.mark.parametrize("batch", [1, 8, 32])
-def test_decoder_step_small(batch):
+# Logits tolerance of the whole-decoder tests: the stated bound for bf16 outputs.  A single
+# bf16 rounding flip of an activation (two correct evaluations that add in a different order
+# differ by such flips) moves a logit by up to ~2e-2 x RMS on these tiny models, so the rows
+# are also checked in aggregate: the bound must hold for 97 % of all logits and no logit may
+# be off by more than 3x the bound.
+LOGIT_TOL = 2e-2
+
+
+def _check_logits(got, want):
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64)) / rms
+    print(f"logits: max err {err.max():.3e} x RMS, {100 * np.mean(err <= LOGIT_TOL):.2f} % within {LOGIT_TOL}")
+    assert np.mean(err <= LOGIT_TOL) >= 0.97
+    assert err.max() <= 3 * LOGIT_TOL
+
+
+@pytest.mark.parametrize("batch", [1, 3, 8, 32])
+def test_decoder_step_small(batch, step_path):
     cfg = inputs.decoder_config(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=512, vocab=2048)
     results, dcache, ocache, dec = _run_decoder(cfg, batch, ctx=70, max_len=96, steps=2)
     for got, want in results:
-        # two layers of bf16 activations: rounding flips compound (see the oracle's own C-vs-NumPy bound)
-        assert dense.max_abs_over_rms(got, want) <= 6e-2
+        _check_logits(got, want)
         assert np.mean(got.argmax(-1) == want.argmax(-1)) >= 0.9
     for li in range(2):
         assert rel_rms_err(host(dcache["k"][li]).astype(np.float32), ocache["k"][li].astype(np.float32)) <= 8e-2
-    assert dec.launches_per_step(batch) > 0
+    if step_path == "stream" and batch <= 8:
+        assert dec.launches_per_step(batch) == 1 and dec.graphs_built() == 0
+    else:
+        assert dec.launches_per_step(batch) > 1
 
 
-def test_decoder_against_reference_fixture(golden_dir):
+@pytest.mark.parametrize("cfgkw,batch,ctx,max_len", [
+    (dict(layers=3, hidden=512, heads=8, kv_heads=2, head_dim=128, inter=1536, vocab=4096), 2, 300, 320),   # G = 4, D = 128
+    (dict(layers=2, hidden=384, heads=8, kv_heads=1, head_dim=128, inter=448, vocab=1008), 1, 5, 8),         # G = 8, ragged K
+    (dict(layers=2, hidden=256, heads=2, kv_heads=2, head_dim=128, inter=512, vocab=512), 4, 0, 16),         # G = 1, pos 0
+    (dict(layers=2, hidden=256, heads=4, kv_heads=4, head_dim=64, inter=256, vocab=528), 2, 1100, 1104),     # long chunks
+])
+def test_decoder_stream_shapes(cfgkw, batch, ctx, max_len):
+    """The single-kernel step over the head-group / head-dim variants it is compiled for,
+    input widths that are no multiple of a record, the first position and long caches."""
+    cfg = inputs.decoder_config(**cfgkw)
+    results, dcache, ocache, dec = _run_decoder(cfg, batch, ctx=ctx, max_len=max_len, steps=2)
+    assert dec.launches_per_step(batch) == 1
+    for got, want in results:
+        _check_logits(got, want)
+    for li in range(cfg["layers"]):
+        assert rel_rms_err(host(dcache["k"][li]).astype(np.float32), ocache["k"][li].astype(np.float32)) <= 8e-2
+        assert rel_rms_err(host(dcache["v"][li]).astype(np.float32), ocache["v"][li].astype(np.float32)) <= 8e-2
+
+
+def test_decoder_against_reference_fixture(golden_dir, step_path):
     """The reference's forward() output (split-half int4 repacked to sequential words)."""
     import torch
     from oracle import quant
@@ -223,13 +311,13 @@ def test_decoder_against_reference_fixture(golden_dir):
     logits = dec.step(dev(z["tokens"][:, 0].astype(np.int32)), torch.tensor([int(z["ctx"])], dtype=torch.int32, device="cuda"))
     torch.cuda.synchronize()
     want = z["logits"]
-    assert dense.max_abs_over_rms(host(logits), want) <= 6e-2
+    _check_logits(host(logits), want)
     assert np.array_equal(host(logits).argmax(-1), want.argmax(-1))
     for li in range(2):
         assert rel_rms_err(host(cache["k"][li]).astype(np.float32), z[f"k_out{li}"].view(bf16).astype(np.float32)) <= 8e-2
 
 
-def test_graph_replay_is_deterministic():
+def test_step_replay_is_deterministic(step_path):
     cfg = inputs.decoder_config(layers=2, hidden=128, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=512)
     import torch
     p = pkg()
@@ -239,6 +327,59 @@ def test_graph_replay_is_deterministic():
     pos = torch.tensor([10], dtype=torch.int32, device="cuda")
     out = torch.empty((4, 512), device="cuda")
     a = dec.step(tok, pos, out).clone()
-    b = dec.step(tok, pos, out).clone()   # replay of the captured graph
+    b = dec.step(tok, pos, out).clone()   # the same step again (a graph replay on the per-operator path)
     torch.cuda.synchronize()
     assert torch.equal(a, b)
+
+
+def test_fresh_tensors_every_step_do_not_grow_the_graph_cache(monkeypatch):
+    """A generate loop hands the step new token / position tensors every time and often a new
+    logits tensor: tokens and position are staged, graphs are keyed by the output pointer and
+    the cache is bounded."""
+    import torch
+    monkeypatch.setenv("B200_DECODER_NO_STREAM", "1")
+    cfg = inputs.decoder_config(layers=2, hidden=128, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=512)
+    p = pkg()
+    params, cache, tokens = inputs.config5(cfg, 2, 3, max_len=128)
+    dec = p.qwen3.Decoder(dev_params(params), {k: [dev(a) for a in v] for k, v in cache.items()}, cfg, max_batch=2)
+    out = torch.empty((2, 512), device="cuda")
+    first = None
+    for i in range(100):
+        tok = dev(tokens.astype(np.int32)).clone()                       # a fresh tensor every step
+        pos = torch.tensor([3], dtype=torch.int32, device="cuda")
+        got = dec.step(tok, pos, out)
+        first = got.clone() if first is None else first
+    torch.cuda.synchronize()
+    assert dec.graphs_built() == 1
+    assert torch.equal(first, out)
+    keep = [torch.empty((2, 512), device="cuda") for _ in range(20)]     # 20 distinct output buffers
+    for o in keep:
+        dec.step(dev(tokens.astype(np.int32)), torch.tensor([3], dtype=torch.int32, device="cuda"), o)
+    torch.cuda.synchronize()
+    assert dec.graphs_built() == 21
+    assert all(torch.equal(first, o) for o in keep)
+    assert p.default_context().error() == 0
+
+
+def test_step_refuses_bad_token_and_position(step_path):
+    """Host-made bad inputs through the guarded paths: nothing faults, nothing is written
+    outside the cache, the status word says INVALID_ARGUMENT."""
+    import torch
+    cfg = inputs.decoder_config(layers=2, hidden=128, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=512)
+    p = pkg()
+    params, cache, tokens = inputs.config5(cfg, 2, 3, max_len=16)
+    for bad_tok, bad_pos in ((700, 3), (5, 16), (-1, 3), (5, -2)):
+        ctx = p.Context(0)
+        dcache = {k: [dev(a) for a in v] for k, v in cache.items()}
+        before = [host(t).copy() for t in dcache["k"] + dcache["v"]]
+        dec = p.qwen3.Decoder(dev_params(params), dcache, cfg, max_batch=2, ctx=ctx)
+        dec.step(torch.tensor([bad_tok, 1], dtype=torch.int32, device="cuda"),
+                 torch.tensor([bad_pos], dtype=torch.int32, device="cuda"))
+        torch.cuda.synchronize()
+        assert ctx.error() == p._lib.INVALID_ARGUMENT
+        assert b"INVALID_ARGUMENT" in p.lib().b200_last_error()
+        if bad_pos != 3:
+            after = [host(t) for t in dcache["k"] + dcache["v"]]
+            assert all(np.array_equal(x.view(np.uint16), y.view(np.uint16)) for x, y in zip(before, after))
+        dec.close()
+        ctx.close()

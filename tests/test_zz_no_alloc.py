@@ -45,6 +45,7 @@ def test_static_scratch_attention_matches_the_allocating_entry_point_twice():
         g, w = host(got).astype(np.float32), host(want).astype(np.float32)
         assert np.isfinite(g).all()
         assert rel_rms_err(g, w) <= 2e-2          # the tolerance the other attention tests use
+        assert np.array_equal(g, w)               # and in fact the same kernels ran: the same bits
     assert ctx.error() == 0
 
 
