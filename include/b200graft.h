@@ -248,6 +248,18 @@ b200_status b200_decoder_step(b200_decoder* dec, b200_stream stream, const int32
 int64_t b200_decoder_launches_per_step(b200_decoder* dec, int batch);
 /* CUDA graphs this decoder has captured so far (0 while every step took the single kernel). */
 int64_t b200_decoder_graphs_built(b200_decoder* dec);
+/* Per-stage tracing of the single-kernel step (≙ METAL_PJRT_TRACE's per-command timing,
+ * metal_pjrt/runtime/metal_runtime.cc:56-59,1671, moved inside the kernel because there is
+ * only one launch to time).  While enabled, thread 0 of every CTA stamps the device's
+ * nanosecond timer four times per stage: 0 the stage may start (grid barrier passed),
+ * 1 its inputs are staged in shared memory, 2 its share of the weight records is consumed,
+ * 3 its outputs are written.  b200_decoder_trace_read copies the stamps of the last step
+ * (uint64 [ctas, stages, 4]; call with out == NULL to learn the sizes) after the caller has
+ * synchronised the stream, and the stage kinds (0 qkv, 1 attention, 2 o, 3 gate_up, 4 down,
+ * 5 LM head; int32 [stages]).  FAILED_PRECONDITION on a decoder without the single kernel. */
+b200_status b200_decoder_trace(b200_decoder* dec, int enable);
+b200_status b200_decoder_trace_read(b200_decoder* dec, uint64_t* out, int64_t capacity, int32_t* ctas,
+                                    int32_t* stages, int32_t* stage_types);
 
 /* Pieces of the step, exported for parity tests (bf16 throughout). */
 /* table bf16 [vocab, hidden].  A token id outside [0, vocab) reads row 0 and reports

@@ -95,6 +95,8 @@ PROTOTYPES = {
     "b200_decoder_step": (_I, [_VP, _VP, _VP, _VP, _VP, _I]),
     "b200_decoder_launches_per_step": (_I64, [_VP, _I]),
     "b200_decoder_graphs_built": (_I64, [_VP]),
+    "b200_decoder_trace": (_I, [_VP, _I]),
+    "b200_decoder_trace_read": (_I, [_VP, _VP, _I64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), _VP]),
     "b200_embed": (_I, [_VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64]),
     "b200_qk_norm_rope_cache": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64,
                                      C.c_float, C.c_float]),

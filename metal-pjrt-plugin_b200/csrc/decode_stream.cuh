@@ -27,5 +27,9 @@ b200_status DecodeStreamStep(DecodeStream* ds, cudaStream_t stream, const int32_
                              float* logits, int32_t* next_token, int batch);
 // Bytes of device memory the repacked weights take.
 size_t DecodeStreamPackedBytes(const DecodeStream* ds);
+// Per-stage tracing (see b200_decoder_trace in the C header).
+b200_status DecodeStreamTrace(DecodeStream* ds, bool enable);
+b200_status DecodeStreamTraceRead(DecodeStream* ds, unsigned long long* out, int64_t capacity, int* ctas, int* stages,
+                                  int* stage_types);
 
 }  // namespace b200

@@ -433,6 +433,19 @@ b200_status b200_decoder_step(b200_decoder* d, b200_stream stream, const int32_t
   return B200_OK;
 }
 
+b200_status b200_decoder_trace(b200_decoder* d, int enable) {
+  if (d == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_decoder_trace: null decoder");
+  std::lock_guard<std::mutex> lock(d->mu);
+  return DecodeStreamTrace(d->stream_path, enable != 0);
+}
+
+b200_status b200_decoder_trace_read(b200_decoder* d, uint64_t* out, int64_t capacity, int32_t* ctas, int32_t* stages,
+                                    int32_t* stage_types) {
+  if (d == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_decoder_trace_read: null decoder");
+  std::lock_guard<std::mutex> lock(d->mu);
+  return DecodeStreamTraceRead(d->stream_path, reinterpret_cast<unsigned long long*>(out), capacity, ctas, stages, stage_types);
+}
+
 int64_t b200_decoder_graphs_built(b200_decoder* d) {
   if (d == nullptr) return 0;
   std::lock_guard<std::mutex> lock(d->mu);

@@ -181,6 +181,22 @@ class Decoder:
         """CUDA graphs captured so far (0 while every step took the single kernel)."""
         return _lib.lib().b200_decoder_graphs_built(self.handle)
 
+    def trace(self, enable=True):
+        """Per-stage time stamps inside the single-kernel step (b200_decoder_trace)."""
+        _lib.check(_lib.lib().b200_decoder_trace(self.handle, 1 if enable else 0))
+
+    def read_trace(self):
+        """(stamps uint64 [ctas, stages, 4] in ns, stage kinds int32 [stages]) of the last
+        traced step; synchronise the stream first."""
+        import numpy as np
+        ctas, stages = C.c_int32(), C.c_int32()
+        _lib.check(_lib.lib().b200_decoder_trace_read(self.handle, None, 0, C.byref(ctas), C.byref(stages), None))
+        out = np.zeros((ctas.value, stages.value, 4), np.uint64)
+        kinds = np.zeros(stages.value, np.int32)
+        _lib.check(_lib.lib().b200_decoder_trace_read(self.handle, out.ctypes.data_as(C.c_void_p), out.size,
+                                                      C.byref(ctas), C.byref(stages), kinds.ctypes.data_as(C.c_void_p)))
+        return out, kinds
+
     def close(self):
         if self.handle:
             _lib.lib().b200_decoder_destroy(self.handle)
