@@ -20,16 +20,15 @@
 // tiles are dealt round-robin to the CTAs, continuing from stage to stage where the previous
 // one stopped, so every CTA streams the same number of bytes over a layer.
 //
-// Consumers (15 warps).  A record is one warp's work.  The nibbles go to the tensor cores as
-// FP8: a byte 0x0q read as e4m3 is exactly q * 2^-9 (the subnormals and the first binade of
-// e4m3 are one evenly spaced run of 16 values), so "widening" is two AND masks and one shift
-// per eight weights, and mma.sync m16n8k32 e4m3 issues four times faster than the bf16 MMA on
-// this GPU.  The activations are split on the fly into two e4m3 terms x1 + x2 (after an exact
-// power-of-two row scale; together they carry the 8 significant bits a bf16 value has) that
-// occupy two of the MMA's eight batch columns, so one MMA multiplies both; the residual error
-// is 2^-17 of the row maximum per element, far below the bf16 rounding of the result.  Scale
-// and offset are applied in f32 per group of 64, sum_k x (s q + b) = s sum_k x q + b sum_k x,
-// with sum_k x taken from the unsplit activations.  The records of a CTA's stream go to
+// Consumers (15 warps).  A record is one warp's work: nibbles are widened to bf16 (128 + q) by
+// one lop3 per pair and fed to mma.sync m16n8k16 with the batch as the 8-wide operand; x
+// lies in shared memory in its natural order (the nibble order inside a record is chosen so
+// that a lane's x fragment is 32 contiguous bytes); scale and offset are applied in f32 per
+// group of 64 exactly as the per-operator kernel does.  (Measured and rejected: the nibbles as
+// e4m3 subnormals through mma.sync m16n8k32 e4m3 with the activations split into two e4m3
+// terms - numerically fine, but on this GPU that MMA costs 30-55 issue cycles as soon as its
+// operands change from one MMA to the next, against ~10 for the bf16 one; and right shifts as
+// multiply-high on the FMA pipe, 4-6 cycles each against ~1.)  The records of a CTA's stream go to
 // its warps round-robin; the partial tiles of a row tile are added in a fixed order after one
 // barrier per stage.  A gate_up tile holds eight gate rows and their eight up rows, so
 // silu(gate) * up is formed where the tile is finished and never makes a round trip.
@@ -54,7 +53,7 @@ constexpr int kNW = 15;                      // consumer warps (with the produce
 constexpr int kConsumers = kNW * 32;
 constexpr int kThreads = kConsumers + 32;    // + the producer warp
 constexpr int kAttnThreads = 256;            // consumer threads that work in the attention stage
-constexpr int kMaxM = 4;                     // batch rows: each takes two of the MMA's eight batch columns
+constexpr int kMaxM = 8;                     // batch rows: the MMA's eight batch columns
 constexpr int kUnitK = 512;                  // inputs per int4 record
 constexpr int kUnitGroups = kUnitK / 64;
 constexpr int kUnitBytes = 16 * kUnitK / 2 + 16 * kUnitGroups * 4;   // 4608
@@ -113,9 +112,7 @@ struct StreamArgs {
   int attn_chunks;
   int NS, NS2;                     // ring slots (int4 records / LM-head units)
   int part_units;                  // partial tiles the reduction buffer holds
-  int xs_pitch;                    // bytes between the e4m3 rows of x in shared memory (two rows per batch row)
-  int xh_pitch;                    // bytes between the bf16 rows of x that the LM head reads
-  int off_tmp;                     // bf16 [M, E] scratch of the RMSNorm staging
+  int xs_pitch;                    // bf16 elements between rows of x in shared memory
   int MP;                          // batch columns kept per partial tile (M rounded up to even)
   int off_xsum, off_part, off_ring;   // byte offsets into dynamic shared memory
   int* status;
@@ -232,7 +229,6 @@ struct Shared {   // the fixed header of dynamic shared memory (kHeaderBytes)
   float red[8][16];
   float redl[8][16];
   float rinv[8];
-  float xfac[kMaxM];   // 2^9 / (row scale of x): turns an e4m3 dot product back into real units
   float rope_cos[64], rope_sin[64];   // cos / sin of pos * inv_freq[i]: the same for every head and layer of a step
   __align__(16) uint32_t zeros[8];    // what the lanes of batch columns beyond M read as their x
   int dead;
@@ -277,37 +273,6 @@ __device__ __forceinline__ void grid_wait(const StreamArgs& a, Shared* sh, int n
 //   plain (o, down): the attention output / silu(gate) * up
 // The grid barrier in front of the stage (number nb, 0 = none) is taken in here.
 // ---------------------------------------------------------------------------------------
-// ---- e4m3 helpers (cvt packs two values: the first operand lands in the upper byte)
-__device__ __forceinline__ uint32_t f2_to_e4m3x2(float lo, float hi) {
-  unsigned short v;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(v) : "f"(hi), "f"(lo));
-  return v;
-}
-__device__ __forceinline__ float2 e4m3x2_to_f2(uint32_t v) {
-  uint32_t h2;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(v)));
-  return __half22float2(*reinterpret_cast<__half2*>(&h2));
-}
-// Eight activations -> eight bytes of x1 and eight bytes of x2 (x * sc = x1 + x2 up to 2^-9 of x1's ulp).
-__device__ __forceinline__ void split8(const float* f, float sc, uint2& x1, uint2& x2) {
-  uint32_t a[4], b[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float v0 = f[2 * j] * sc, v1 = f[2 * j + 1] * sc;
-    a[j] = f2_to_e4m3x2(v0, v1);
-    const float2 back = e4m3x2_to_f2(a[j]);
-    b[j] = f2_to_e4m3x2(v0 - back.x, v1 - back.y);
-  }
-  x1 = make_uint2(a[0] | (a[1] << 16), a[2] | (a[3] << 16));
-  x2 = make_uint2(b[0] | (b[1] << 16), b[2] | (b[3] << 16));
-}
-// Power of two that brings a row whose largest magnitude is `mx` just below e4m3's largest finite value.
-__device__ __forceinline__ float row_scale(float mx) {
-  if (!(mx > 0.0f) || !(mx < 3.0e38f)) return 1.0f;
-  int e;
-  frexpf(mx, &e);               // mx = f * 2^e, f in [0.5, 1)
-  return ldexpf(1.0f, 8 - e);   // mx * scale in [128, 256)
-}
 __device__ __forceinline__ void group_sums(float* xsum, const float* v8, int m, int piece, int lane) {
   float s = 0.0f;
 #pragma unroll
@@ -315,103 +280,62 @@ __device__ __forceinline__ void group_sums(float* xsum, const float* v8, int m, 
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
   s += __shfl_xor_sync(0xffffffffu, s, 4);
-  if ((lane & 7) == 0) xsum[(piece >> 3) * kMaxM + m] = s;
+  if ((lane & 7) == 0) xsum[(piece >> 3) * 8 + m] = s;
 }
 
 __device__ void stage_inputs(const StreamArgs& a, const Stage& st, Shared* sh, uint8_t* smem, int xcur, bool first_layer,
                              bool work, int nb, int si, int tid) {
   const int lane = tid & 31, warp = tid >> 5;
-  uint8_t* xs = smem + kHeaderBytes;                                            // e4m3 rows (2 per batch row), or the LM head's bf16 rows
-  __nv_bfloat16* tmpx = reinterpret_cast<__nv_bfloat16*>(smem + a.off_tmp);     // bf16 [M, K] of the RMSNorm staging
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem + kHeaderBytes);
   float* xsum = reinterpret_cast<float*>(smem + a.off_xsum);
-  const bool head = st.type == kHead;
-  const int K = st.K, Kpad = st.C * (head ? kHeadUnitK : kUnitK);
-  const int nvK = K / 8;       // 8-value pieces of a row
+  const int K = st.K, Kpad = st.C * (st.type == kHead ? kHeadUnitK : kUnitK);
+  const int pitch = a.xs_pitch;
+  const int nvK = K / 8;       // 16-byte pieces of a row
   const int nvec = Kpad / 8;   // ... the zero tail included (a multiple of 64 pieces)
-  const bool norm = st.type == kQkv || st.type == kGateUp || head;
-  // one finished piece: the two e4m3 terms (or, for the LM head, the bf16 values) and the group sums
-  auto emit = [&](int m, int v, const float* f, float sc) {
-    if (head) {
-      *reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * a.xh_pitch + 16 * v) = pack8(f);
-    } else {
-      uint2 x1, x2;
-      split8(f, sc, x1, x2);
-      *reinterpret_cast<uint2*>(xs + static_cast<size_t>(2 * m) * a.xs_pitch + 8 * v) = x1;
-      *reinterpret_cast<uint2*>(xs + static_cast<size_t>(2 * m + 1) * a.xs_pitch + 8 * v) = x2;
-      group_sums(xsum, f, m, v, lane);
-    }
-  };
+  const bool norm = st.type == kQkv || st.type == kGateUp || st.type == kHead;
   if (!norm) {
     grid_wait(a, sh, nb, tid);
     stamp(a, si, 0, tid);
     if (!work) return;
     const __nv_bfloat16* src = st.type == kO ? a.attn : a.hmlp;
-    // rows of up to 4 * 480 pieces are held in registers between the two passes (maximum, then split)
-    const bool in_regs = nvK <= 4 * kConsumers;
     for (int m = 0; m < a.M; ++m) {
-      const uint4* row = reinterpret_cast<const uint4*>(src + static_cast<long long>(m) * K);
-      uint4 raw[4];
-      float mx = 0.0f;
+      for (int v0 = 0; v0 < nvec; v0 += 4 * kConsumers) {
+        uint4 raw[4];
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {   // all the loads in flight together
-        const int v = it * kConsumers + tid;
-        raw[it] = v < nvK ? __ldcg(row + v) : make_uint4(0, 0, 0, 0);
-      }
+        for (int it = 0; it < 4; ++it) {   // all the loads of the round in flight together
+          const int v = v0 + it * kConsumers + tid;
+          raw[it] = v < nvK ? __ldcg(reinterpret_cast<const uint4*>(src + static_cast<long long>(m) * K) + v) : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        float f[8];
-        unpack8(raw[it], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-      }
-      for (int v = 4 * kConsumers + tid; v < nvK; v += kConsumers) {
-        float f[8];
-        unpack8(__ldcg(row + v), f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
-      }
-      mx = warp_max(mx);
-      if (lane == 0) sh->red[m][warp] = mx;
-      consumer_bar();
-      float all = sh->red[m][0];
-#pragma unroll
-      for (int w = 1; w < kNW; ++w) all = fmaxf(all, sh->red[m][w]);
-      const float sc = row_scale(all);
-      if (tid == 0) sh->xfac[m] = 512.0f / sc;
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int v = it * kConsumers + tid;
-        if (v < nvec) {   // whole warps: nvec and the warp's first piece are multiples of 32
-          float f[8];
-          unpack8(raw[it], f);
-          emit(m, v, f, sc);
+        for (int it = 0; it < 4; ++it) {
+          const int v = v0 + it * kConsumers + tid;
+          if (v < nvec) {   // whole warps: nvec and the warp's first piece are multiples of 32
+            float f[8];
+            unpack8(raw[it], f);
+            *reinterpret_cast<uint4*>(xs + m * pitch + 8 * v) = raw[it];
+            group_sums(xsum, f, m, v, lane);
+          }
         }
       }
-      for (int v = 4 * kConsumers + tid; v < nvec; v += kConsumers) {
-        float f[8];
-        unpack8(v < nvK ? __ldcg(row + v) : make_uint4(0, 0, 0, 0), f);
-        emit(m, v, f, sc);
-      }
-      (void)in_regs;
     }
     consumer_bar();
     return;
   }
 
   // ---- residual + RMSNorm
-  // what does not depend on the stage before: the old residual rows (a thread's first two pieces
-  // of each) and the gain
-  uint4 xo[kMaxM][2], gn[2];
+  // what does not depend on the stage before: the old residual rows (up to 4 of them; a thread's
+  // first two pieces of each) and the gain
+  uint4 xo[4][2], gn[2];
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
     const int v = it * kConsumers + tid;
     gn[it] = make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int m = 0; m < kMaxM; ++m) xo[m][it] = make_uint4(0, 0, 0, 0);
+    for (int m = 0; m < 4; ++m) xo[m][it] = make_uint4(0, 0, 0, 0);
     if (work && v < nvK) {
       gn[it] = __ldg(reinterpret_cast<const uint4*>(st.gain) + v);
 #pragma unroll
-      for (int m = 0; m < kMaxM; ++m) {
+      for (int m = 0; m < 4; ++m) {
         if (m < a.M) {
           const __nv_bfloat16* xo_row;
           if (first_layer) {
@@ -433,12 +357,10 @@ __device__ void stage_inputs(const StreamArgs& a, const Stage& st, Shared* sh, u
     const long long tok = a.tokens[tid];
     if (tok < 0 || tok >= a.vocab_full) report_status(a.status, B200_INVALID_ARGUMENT, 501);
   }
-  // one piece: new residual value, kept in shared memory (and written by CTA 0 to the other
-  // residual buffer); its contribution to the row's sum of squares and to max |x * gain|
-  auto piece = [&](int m, int v, const uint4& xold, const uint4& gain8, float& ss, float& ug) {
-    float f[8], gq[8];
+  // one piece: new residual value, written to shared memory (and by CTA 0 to the other residual buffer)
+  auto piece = [&](int m, int v, const uint4& xold, float& ss) {
+    float f[8];
     unpack8(xold, f);
-    unpack8(gain8, gq);
     if (!first_layer) {
       const float4 y0 = __ldcg(reinterpret_cast<const float4*>(a.y + static_cast<long long>(m) * K) + 2 * v);
       const float4 y1 = __ldcg(reinterpret_cast<const float4*>(a.y + static_cast<long long>(m) * K) + 2 * v + 1);
@@ -447,61 +369,54 @@ __device__ void stage_inputs(const StreamArgs& a, const Stage& st, Shared* sh, u
       for (int j = 0; j < 8; ++j) f[j] = bf16_round(f[j] + bf16_round(yy[j]));
     }
     const uint4 packed = pack8(f);
-    *reinterpret_cast<uint4*>(tmpx + static_cast<size_t>(m) * K + 8 * v) = packed;
-    if (blockIdx.x == 0 && !head) *(reinterpret_cast<uint4*>(a.x[xcur ^ 1] + static_cast<long long>(m) * K) + v) = packed;
+    *reinterpret_cast<uint4*>(xs + m * pitch + 8 * v) = packed;
+    if (blockIdx.x == 0 && st.type != kHead) *(reinterpret_cast<uint4*>(a.x[xcur ^ 1] + static_cast<long long>(m) * K) + v) = packed;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      ss = fmaf(f[j], f[j], ss);
-      ug = fmaxf(ug, fabsf(f[j] * gq[j]));
-    }
+    for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
   };
 #pragma unroll
-  for (int m = 0; m < kMaxM; ++m) {
+  for (int m = 0; m < 4; ++m) {
     if (m < a.M) {
-      float ss = 0.0f, ug = 0.0f;
+      float ss = 0.0f;
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
         const int v = it * kConsumers + tid;
-        if (v < nvK) piece(m, v, xo[m][it], gn[it], ss, ug);
+        if (v < nvK) piece(m, v, xo[m][it], ss);
       }
       for (int v = 2 * kConsumers + tid; v < nvK; v += kConsumers) {   // rows longer than 7680
         const __nv_bfloat16* xo_row = first_layer ? a.embed + static_cast<long long>(max(0, min(a.tokens[m], static_cast<int>(a.vocab_full - 1)))) * K
                                                   : a.x[xcur] + static_cast<long long>(m) * K;
-        piece(m, v, __ldcg(reinterpret_cast<const uint4*>(xo_row) + v), __ldg(reinterpret_cast<const uint4*>(st.gain) + v), ss, ug);
+        piece(m, v, __ldcg(reinterpret_cast<const uint4*>(xo_row) + v), ss);
       }
       ss = warp_sum(ss);
-      ug = warp_max(ug);
-      if (lane == 0) {
-        sh->red[m][warp] = ss;
-        sh->redl[m][warp] = ug;
-      }
+      if (lane == 0) sh->red[m][warp] = ss;
     }
+  }
+  for (int m = 4; m < a.M; ++m) {   // rows beyond the four kept in registers
+    float ss = 0.0f;
+    const __nv_bfloat16* xo_row = first_layer ? a.embed + static_cast<long long>(max(0, min(a.tokens[m], static_cast<int>(a.vocab_full - 1)))) * K
+                                              : a.x[xcur] + static_cast<long long>(m) * K;
+    for (int v = tid; v < nvK; v += kConsumers) piece(m, v, __ldcg(reinterpret_cast<const uint4*>(xo_row) + v), ss);
+    ss = warp_sum(ss);
+    if (lane == 0) sh->red[m][warp] = ss;
   }
   consumer_bar();
   if (tid < a.M) {
-    float t = 0.0f, u = 0.0f;
+    float t = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kNW; ++w) {
-      t += sh->red[tid][w];
-      u = fmaxf(u, sh->redl[tid][w]);
-    }
-    const float r = 1.0f / sqrtf(t / static_cast<float>(K) + a.eps);
-    sh->rinv[tid] = r;
-    // |x * r * gain| <= max |x * gain| * r (a hair above after the roundings: 1.01 covers them)
-    const float sc = row_scale(1.01f * u * r);
-    sh->rinv[4 + tid] = sc;
-    sh->xfac[tid] = 512.0f / sc;
+    for (int w = 0; w < kNW; ++w) t += sh->red[tid][w];
+    sh->rinv[tid] = 1.0f / sqrtf(t / static_cast<float>(K) + a.eps);
   }
   consumer_bar();
-  // pass 2: normalise (every thread revisits the pieces it wrote), split, sum
+  // pass 2: normalise in place (every thread revisits the pieces it wrote)
   for (int m = 0; m < a.M; ++m) {
-    const float r = sh->rinv[m], sc = sh->rinv[4 + m];
+    const float r = sh->rinv[m];
     int it = 0;
     for (int v = tid; v < nvec; v += kConsumers, ++it) {
       float f[8];
       if (v < nvK) {
         float g[8];
-        unpack8(*reinterpret_cast<const uint4*>(tmpx + static_cast<size_t>(m) * K + 8 * v), f);
+        unpack8(*reinterpret_cast<const uint4*>(xs + m * pitch + 8 * v), f);
         unpack8(it == 0 ? gn[0] : (it == 1 ? gn[1] : __ldg(reinterpret_cast<const uint4*>(st.gain) + v)), g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = bf16_round((f[j] * r) * g[j]);
@@ -509,27 +424,30 @@ __device__ void stage_inputs(const StreamArgs& a, const Stage& st, Shared* sh, u
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = 0.0f;
       }
-      emit(m, v, f, sc);
+      *reinterpret_cast<uint4*>(xs + m * pitch + 8 * v) = pack8(f);
+      group_sums(xsum, f, m, v, lane);
     }
   }
   consumer_bar();
 }
 
 // ---------------------------------------------------------------------------------------
-// One int4 record: 16 rows x 512 inputs against the batch.  Lane (g, t): weight rows g / g + 8,
-// batch row t (its x1 / x2 terms are the MMA's batch columns 2t / 2t + 1, which is also how the
-// accumulator fragment is laid out: c0 + c1 is row g's full product, c2 + c3 row g + 8's).
-// a1[2]: sum_g s_g * (e4m3 dot product of group g) for rows g / g + 8; a2[2]: sum_g b_g * sum_k x.
+// One int4 record: 16 rows x 512 inputs against the batch.  acc: rows g / g+8, batch columns
+// 2t / 2t+1 (the m16n8k16 accumulator fragment).
 //
 // The loads and MMAs are volatile asms in a hand-written software pipeline: per group
 //   loads of group gi + 1 | widening of group gi | MMAs of group gi | scaling of group gi - 1
-// so that every warp's instruction stream alternates between the pipes.
+// so that every warp's instruction stream alternates between the pipes and nothing waits for
+// the result of the instruction just before it.
+// Issue cost per group and scheduler, from microbenchmarks on this GPU: 16 lop3 at 2 cycles,
+// 12 shifts at ~1, four bf16 MMAs at 8-12, the loads and the f32 arithmetic ~25: about 100
+// cycles, against the 102 that the measured HBM rate leaves for 16 rows x 64 inputs.
 // ---------------------------------------------------------------------------------------
 struct GroupRegs {
-  uint4 w;      // nibbles: rows g / g + 8, 16 inputs each (two words per row)
-  uint2 sb;     // (scale, offset) of rows g / g + 8
-  uint4 x;      // 16 e4m3 bytes of this lane's batch column (x1 or x2 of a batch row)
-  float xs;     // sum of x over the group for batch row t
+  uint4 w;       // nibbles: rows g / g + 8, 16 inputs each
+  uint2 sb;      // (scale, offset) of rows g / g + 8
+  uint4 x0, x1;  // 16 inputs of the lane's batch column
+  float2 xs2;    // sum of x over the group for batch columns 2t, 2t + 1
 };
 __device__ __forceinline__ uint4 vlds128(uint32_t addr) {
   uint4 v;
@@ -554,9 +472,9 @@ __device__ __forceinline__ uint2 vlds64(uint32_t addr) {
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ float vlds32f(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+__device__ __forceinline__ float2 vlds64f(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ void vmma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -564,36 +482,33 @@ __device__ __forceinline__ void vmma(float (&c)[4], uint32_t a0, uint32_t a1, ui
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// d = a . b over 32 e4m3 inputs, no accumulator input
-__device__ __forceinline__ void vmma8_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+__device__ __forceinline__ void vmma_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
-__device__ __forceinline__ void vmma8(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
-// xaddr: this lane's 16 bytes of group 0 (row 2t' + part of the e4m3 x, where the lane's
-// batch column g = 2t' + part); xon: 0 in the lanes of batch columns beyond 2M (they read nothing).
+// xstep: 128 (bytes of x per group) in the lanes of a real batch column, 0 in the others (which
+// load nothing and multiply zeros).
 template <int MODE = 0>   // MODE > 0: measurement builds that leave parts of the work out (wrong results)
-__device__ __forceinline__ void int4_record(uint32_t rec, uint32_t xaddr, uint32_t xon, uint32_t xsum_addr, int lane,
-                                            float (&a1)[2], float (&a2)[2]) {
+__device__ __forceinline__ void int4_record(uint32_t rec, uint32_t xaddr, uint32_t xstep, uint32_t xsum_addr, int lane,
+                                            float (&acc)[4]) {
   const int g = lane >> 2;
   auto load = [&](int gi, GroupRegs& r) {
     r.w = vlds128(rec + gi * 512 + lane * 16);
     r.sb = vlds64(rec + 4096 + gi * 64 + g * 8);
-    r.x = vlds128_if(xaddr + gi * 64, xon);
-    r.xs = vlds32f(xsum_addr + gi * (kMaxM * 4));
+    r.x0 = vlds128_if(xaddr + gi * xstep, xstep);
+    r.x1 = vlds128_if(xaddr + gi * xstep + 16, xstep);
+    r.xs2 = vlds64f(xsum_addr + gi * 32);
   };
-  auto scale = [&](const float (&tmp)[4], const uint2& sb, float xs) {
+  auto scale = [&](const float (&tmp)[4], const uint2& sb, const float2& xs2) {
+    // sum_k x (s q + b) = s * sum_k x (128 + q) + (b - 128 s) * sum_k x
     const float s0 = bf16_lo(sb.x), b0 = bf16_hi(sb.x), s1 = bf16_lo(sb.y), b1 = bf16_hi(sb.y);
-    a1[0] = fmaf(s0, tmp[0] + tmp[1], a1[0]);
-    a1[1] = fmaf(s1, tmp[2] + tmp[3], a1[1]);
-    a2[0] = fmaf(b0, xs, a2[0]);
-    a2[1] = fmaf(b1, xs, a2[1]);
+    const float o0 = fmaf(-128.0f, s0, b0), o1 = fmaf(-128.0f, s1, b1);
+    acc[0] = fmaf(s0, tmp[0], fmaf(o0, xs2.x, acc[0]));
+    acc[1] = fmaf(s0, tmp[1], fmaf(o0, xs2.y, acc[1]));
+    acc[2] = fmaf(s1, tmp[2], fmaf(o1, xs2.x, acc[2]));
+    acc[3] = fmaf(s1, tmp[3], fmaf(o1, xs2.y, acc[3]));
   };
   GroupRegs r[kUnitGroups];
   float tmp[kUnitGroups][4];
@@ -603,28 +518,39 @@ __device__ __forceinline__ void int4_record(uint32_t rec, uint32_t xaddr, uint32
     if (gi + 1 < kUnitGroups) load(gi + 1, r[gi + 1]);
     const uint4 w = r[gi].w;
     if (MODE == 2) {   // loads only
-      a1[0] += __uint_as_float((w.x ^ w.y ^ w.z ^ w.w ^ r[gi].sb.x ^ r[gi].sb.y ^ r[gi].x.x ^ r[gi].x.y ^ r[gi].x.z ^ r[gi].x.w) & 0x3fffffffu) + r[gi].xs;
+      acc[0] += __uint_as_float((w.x ^ w.y ^ w.z ^ w.w ^ r[gi].sb.x ^ r[gi].sb.y ^ r[gi].x0.x ^ r[gi].x0.y ^ r[gi].x0.z ^ r[gi].x0.w ^
+                                 r[gi].x1.x ^ r[gi].x1.y ^ r[gi].x1.z ^ r[gi].x1.w) & 0x3fffffffu) + r[gi].xs2.x + r[gi].xs2.y;
       continue;
     }
-    // a byte 0x0q is the e4m3 value q * 2^-9: low nibbles are inputs +0..3, high nibbles inputs +4..7
-    const uint32_t l0 = w.x & 0x0f0f0f0fu, h0 = (w.x >> 4) & 0x0f0f0f0fu;
-    const uint32_t l1 = w.y & 0x0f0f0f0fu, h1 = (w.y >> 4) & 0x0f0f0f0fu;
-    const uint32_t m0 = w.z & 0x0f0f0f0fu, n0 = (w.z >> 4) & 0x0f0f0f0fu;
-    const uint32_t m1 = w.w & 0x0f0f0f0fu, n1 = (w.w >> 4) & 0x0f0f0f0fu;
+    uint32_t a0[8], a1[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      a0[q] = lop3_and_or(q == 0 ? w.x : shr4(w.x, q), 0x000f000fu, 0x43004300u);   // bf16 (128 + q) pairs
+      a0[4 + q] = lop3_and_or(q == 0 ? w.y : shr4(w.y, q), 0x000f000fu, 0x43004300u);
+      a1[q] = lop3_and_or(q == 0 ? w.z : shr4(w.z, q), 0x000f000fu, 0x43004300u);
+      a1[4 + q] = lop3_and_or(q == 0 ? w.w : shr4(w.w, q), 0x000f000fu, 0x43004300u);
+    }
     if (MODE == 3) {   // loads + widening
-      a1[0] += __uint_as_float((l0 ^ h0 ^ l1 ^ h1 ^ m0 ^ n0 ^ m1 ^ n1 ^ r[gi].sb.x ^ r[gi].sb.y ^ r[gi].x.x ^ r[gi].x.y ^ r[gi].x.z ^ r[gi].x.w) & 0x3fffffffu) + r[gi].xs;
+      uint32_t z = r[gi].sb.x ^ r[gi].sb.y ^ r[gi].x0.x ^ r[gi].x0.y ^ r[gi].x0.z ^ r[gi].x0.w ^ r[gi].x1.x ^ r[gi].x1.y ^ r[gi].x1.z ^ r[gi].x1.w;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) z ^= a0[q] ^ a1[q];
+      acc[0] += __uint_as_float(z & 0x3fffffffu) + r[gi].xs2.x + r[gi].xs2.y;
       continue;
     }
-    vmma8_z(tmp[gi], l0, m0, h0, n0, r[gi].x.x, r[gi].x.y);
-    vmma8(tmp[gi], l1, m1, h1, n1, r[gi].x.z, r[gi].x.w);
+    vmma_z(tmp[gi], a0[0], a1[0], a0[1], a1[1], r[gi].x0.x, r[gi].x0.y);
+    vmma(tmp[gi], a0[2], a1[2], a0[3], a1[3], r[gi].x0.z, r[gi].x0.w);
+    vmma(tmp[gi], a0[4], a1[4], a0[5], a1[5], r[gi].x1.x, r[gi].x1.y);
+    vmma(tmp[gi], a0[6], a1[6], a0[7], a1[7], r[gi].x1.z, r[gi].x1.w);
     if (MODE == 4) {   // no scale / offset arithmetic
-      a1[0] += tmp[gi][0] + tmp[gi][1] + __uint_as_float((r[gi].sb.x ^ r[gi].sb.y) & 0x3fffffffu) + r[gi].xs;
-      a1[1] += tmp[gi][2] + tmp[gi][3];
+      acc[0] += tmp[gi][0] + __uint_as_float((r[gi].sb.x ^ r[gi].sb.y) & 0x3fffffffu) + r[gi].xs2.x;
+      acc[1] += tmp[gi][1] + r[gi].xs2.y;
+      acc[2] += tmp[gi][2];
+      acc[3] += tmp[gi][3];
       continue;
     }
-    if (gi > 0) scale(tmp[gi - 1], r[gi - 1].sb, r[gi - 1].xs);   // the MMAs of the group before have had a group's time to finish
+    if (gi > 0) scale(tmp[gi - 1], r[gi - 1].sb, r[gi - 1].xs2);   // the MMAs of the group before have had a group's time to finish
   }
-  if (MODE == 0) scale(tmp[kUnitGroups - 1], r[kUnitGroups - 1].sb, r[kUnitGroups - 1].xs);
+  if (MODE == 0) scale(tmp[kUnitGroups - 1], r[kUnitGroups - 1].sb, r[kUnitGroups - 1].xs2);
 }
 
 // 8 bf16 rows x `groups` groups of 64 inputs (one LM-head unit), accumulated into acc[0..1] (rows
@@ -1099,13 +1025,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(const Stream
   const uint32_t xs0 = smem_u32(smem + kHeaderBytes);
   const uint32_t xsum0 = smem_u32(smem + a.off_xsum);
   float* part = reinterpret_cast<float*>(smem + a.off_part);
-  // int4 records: this lane's batch column g is term (g & 1) of batch row g / 2
-  const uint32_t xon = g < 2 * a.M ? 1u : 0u;
-  const uint32_t x8_lane = xs0 + static_cast<uint32_t>(g * a.xs_pitch + t * 16);
-  // LM head (bf16 rows): batch row g
   const bool have_x = g < a.M;
-  const uint32_t x_lane = have_x ? xs0 + static_cast<uint32_t>(g * a.xh_pitch + t * 32) : smem_u32(sh->zeros);
+  const uint32_t x_lane = have_x ? xs0 + static_cast<uint32_t>(g * a.xs_pitch * 2 + t * 32) : smem_u32(sh->zeros);
   const uint32_t xstep = have_x ? 128u : 0u;                // bytes of x per group
+  const uint32_t xchunk = have_x ? kUnitK * 2u : 0u;        // ... per record
   const uint32_t xchunk2 = have_x ? kHeadUnitK * 2u : 0u;   // ... per LM-head unit
   // this warp's private part of the rings
   const int k1 = a.NS / kNW, r1 = a.NS % kNW;
@@ -1152,23 +1075,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(const Stream
           sh->dead = 1;
         }
         const int chunk = j % st.C;
-        float a1[2] = {0.0f, 0.0f}, a2[2] = {0.0f, 0.0f};
-        uint32_t rec = ring0 + static_cast<uint32_t>(s) * kUnitBytes, xa = x8_lane + chunk * kUnitK;
-        uint32_t xsa = xsum0 + static_cast<uint32_t>((chunk * kUnitGroups * kMaxM + t) * 4);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        uint32_t rec = ring0 + static_cast<uint32_t>(s) * kUnitBytes, xa = x_lane + chunk * xchunk;
+        uint32_t xsa = xsum0 + static_cast<uint32_t>((chunk * kUnitGroups * 8 + 2 * t) * 4);
         pin_addresses(rec, xa, xsa);
-        if (a.ablate == 0) int4_record<0>(rec, xa, xon, xsa, lane, a1, a2);
-        else if (a.ablate == 2) int4_record<2>(rec, xa, xon, xsa, lane, a1, a2);
-        else if (a.ablate == 3) int4_record<3>(rec, xa, xon, xsa, lane, a1, a2);
-        else if (a.ablate == 4) int4_record<4>(rec, xa, xon, xsa, lane, a1, a2);
-        const float fac = sh->xfac[t];   // (written in the staging of this stage, before a consumer barrier)
-        const float acc[4] = {fmaf(fac, a1[0], a2[0]), fmaf(fac, a1[1], a2[1]), 0.0f, 0.0f};
+        if (a.ablate == 0) int4_record<0>(rec, xa, xstep, xsa, lane, acc);
+        else if (a.ablate == 2) int4_record<2>(rec, xa, xstep, xsa, lane, acc);
+        else if (a.ablate == 3) int4_record<3>(rec, xa, xstep, xsa, lane, acc);
+        else if (a.ablate == 4) int4_record<4>(rec, xa, xstep, xsa, lane, acc);
         pin_results(acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->empty[s]);
-        if (t < a.M) {
+        if (2 * t < a.MP) {
           float* pt = part + j * 16 * a.MP;   // [16 rows][MP batch columns]
-          pt[g * a.MP + t] = acc[0];
-          pt[(g + 8) * a.MP + t] = acc[1];
+          *reinterpret_cast<float2*>(pt + g * a.MP + 2 * t) = make_float2(acc[0], acc[1]);
+          *reinterpret_cast<float2*>(pt + (g + 8) * a.MP + 2 * t) = make_float2(acc[2], acc[3]);
         }
       }
       ubase += total;
@@ -1270,18 +1191,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(const Stream
 // Source: q uint32 [N, K/8] (element k = 8i + j at bits 4j..4j+3), scale / offset bf16
 // [N, K/64].  Block (tile, chunk) writes its 4608-byte record:
 //   weights: group gi, lane (g, t): four words {row g: inputs 16t..16t+7, 16t+8..16t+15;
-//            row g+8: the same}, byte i of a word = input i in its low nibble, input i + 4 in
-//            its high nibble (so that w & 0x0f0f0f0f and (w >> 4) & 0x0f0f0f0f are four
-//            consecutive inputs each, already in e4m3 form);
+//            row g+8: the same}, nibble r of a word = input 2r, nibble r+4 = input 2r+1
+//            (so that one lop3 yields the bf16 pair of two ADJACENT inputs);
 //   then per group gi and g: {scale[g], offset[g], scale[g+8], offset[g+8]} bf16.
 // Groups beyond K are zero.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t pair_nibbles(uint32_t w) {   // w: inputs 0..7 at bits 4i; out: byte i = input i | input (i + 4) << 4
+__device__ __forceinline__ uint32_t pair_nibbles(uint32_t w) {
   uint32_t o = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    o |= ((w >> (4 * i)) & 15u) << (8 * i);
-    o |= ((w >> (16 + 4 * i)) & 15u) << (8 * i + 4);
+  for (int r = 0; r < 4; ++r) {
+    o |= ((w >> (8 * r)) & 15u) << (4 * r);              // input 2r
+    o |= ((w >> (8 * r + 4)) & 15u) << (16 + 4 * r);     // input 2r + 1
   }
   return o;
 }
@@ -1383,19 +1303,16 @@ cudaError_t AllocInto(DecodeStream* ds, T** p, size_t bytes) {
 // Shared-memory carve-up for a batch; false when fewer than the minimum slots would remain.
 bool Layout(const DecodeStream* ds, int M, int max_smem, StreamArgs* a, size_t* total) {
   if (M > kMaxM) return false;
-  a->xs_pitch = ds->kmax + 16;                                         // e4m3 rows, two per batch row
-  a->xh_pitch = ((ds->cfg.hidden + kHeadUnitK - 1) / kHeadUnitK * kHeadUnitK + 8) * 2;   // the LM head's bf16 rows
-  const size_t xs = std::max(static_cast<size_t>(2 * M) * a->xs_pitch, static_cast<size_t>(M) * a->xh_pitch);
+  a->xs_pitch = ds->kmax + 8;
+  const size_t xs = static_cast<size_t>(M) * a->xs_pitch * 2;
   size_t off = kHeaderBytes + ((xs + 127) & ~static_cast<size_t>(127));
   // the attention scratch lives in the x area: make sure it fits
   const int D = ds->cfg.head_dim, Gq = ds->group;
   const size_t attn = static_cast<size_t>(Gq * 2 * (D / 2 + 4) + Gq * kAttnWindow + 2 * (D / 2 + 4) + D +
                                           (kAttnThreads / D) * Gq * D + Gq * (kMaxChunks + 1)) * 4;
   off = std::max(off, kHeaderBytes + ((attn + 127) & ~static_cast<size_t>(127)));
-  a->off_tmp = static_cast<int>(off);
-  off += (static_cast<size_t>(M) * ds->cfg.hidden * 2 + 127) & ~static_cast<size_t>(127);
   a->off_xsum = static_cast<int>(off);
-  off += static_cast<size_t>(ds->kmax / 64) * kMaxM * 4;
+  off += static_cast<size_t>(ds->kmax / 64) * 8 * 4;
   a->off_part = static_cast<int>(off);
   a->MP = (M + 1) & ~1;
   off += static_cast<size_t>(ds->part_units) * 16 * a->MP * 4;

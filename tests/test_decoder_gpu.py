@@ -262,7 +262,7 @@ def test_decoder_step_small(batch, step_path):
         assert np.mean(got.argmax(-1) == want.argmax(-1)) >= 0.9
     for li in range(2):
         assert rel_rms_err(host(dcache["k"][li]).astype(np.float32), ocache["k"][li].astype(np.float32)) <= 8e-2
-    if step_path == "stream" and batch <= 4:   # the single kernel takes up to four rows
+    if step_path == "stream" and batch <= 8:   # the single kernel takes up to eight rows where they fit shared memory
         assert dec.launches_per_step(batch) == 1 and dec.graphs_built() == 0
     else:
         assert dec.launches_per_step(batch) > 1
