@@ -233,15 +233,17 @@ void b200_decoder_destroy(b200_decoder* dec);
 /* tokens: device int32 [batch]; pos: device int32 [1] (position of the new token,
  * every sequence the same, qwen3.py:356); logits: device f32 [batch, vocab_total]
  * (with tp: the all-gathered logits, rank-major).  Enqueues on `stream`.
- * On one GPU and up to a few rows the whole step is ONE persistent kernel that reads
- * tokens / pos / logits pointers afresh at every call.  Otherwise the step is a sequence
- * of kernels captured into a CUDA graph: tokens and pos are copied into decoder-owned
- * buffers first, a graph is kept per (batch, logits pointer) - pass the same logits buffer
- * every step to replay one graph - and at most 8 graphs are kept (least recently used out).
- * Calls on one decoder are serialised by a mutex; use one decoder per host thread to overlap.
- * The persistent kernel copies the int4 projections once, at b200_decoder_create, into its
- * own streaming layout (a second copy of those weights in device memory; when that
- * allocation fails the decoder silently keeps the kernel-per-operator path). */
+ * The step is a sequence of kernels captured into a CUDA graph: tokens and pos are copied
+ * into decoder-owned buffers first, a graph is kept per (batch, logits pointer) - pass the
+ * same logits buffer every step to replay one graph - and at most 8 graphs are kept (least
+ * recently used out).  Calls on one decoder are serialised by a mutex; use one decoder per
+ * host thread to overlap.
+ * With B200_DECODER_STREAM=1 in the environment at b200_decoder_create, one GPU and up to a
+ * few rows, the whole step is instead ONE persistent kernel that reads the tokens / pos /
+ * logits pointers afresh at every call.  It copies the int4 projections once, at creation,
+ * into its own streaming layout (a second copy of those weights in device memory; when
+ * that allocation fails the decoder keeps the graph).  It is slower than the graph today
+ * (2.5 against 2.2 ms per step on the Qwen3-8B shape at batch 1) and is kept as an option. */
 b200_status b200_decoder_step(b200_decoder* dec, b200_stream stream, const int32_t* tokens,
                               const int32_t* pos, float* logits, int batch);
 /* Kernels enqueued by one step at this batch size (1, or the graph's node count). */

@@ -1,11 +1,11 @@
 // One decode step of the Qwen3-shaped int4 decoder
 // (examples/llm/qwen3.py:334-390 with T = 1).  Two implementations:
-//   * one persistent kernel for the whole step (decode_stream.cu) where the
-//     shapes and the batch allow it (one GPU, a few rows);
-//   * otherwise a fixed sequence of this library's kernels on one stream,
-//     captured once per batch size into a CUDA graph (the launches carry
-//     programmatic-dependent-launch edges, so each projection's weight stream
-//     starts while the kernel before it drains).
+//   * a fixed sequence of this library's kernels on one stream, captured once
+//     per batch size into a CUDA graph (the launches carry programmatic-
+//     dependent-launch edges, so each projection's weight stream starts while
+//     the kernel before it drains): the default;
+//   * one persistent kernel for the whole step (decode_stream.cu), on request
+//     (B200_DECODER_STREAM=1), where the shapes and the batch allow it.
 //
 // With a tensor-parallel group the projections are sharded Megatron-style:
 // qkv and gate_up by output rows (heads / intermediate columns stay local, as
@@ -334,8 +334,12 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
     b200_decoder_destroy(d);
     return s;
   }
-  // B200_DECODER_NO_STREAM=1 keeps the kernel-per-operator path (an A/B switch)
-  if (!EnvFlag("B200_DECODER_NO_STREAM")) {
+  // B200_DECODER_STREAM=1 selects the single persistent kernel where it applies.  It is not the
+  // default: measured on the Qwen3-8B shape it takes 2.5 ms per step at batch 1 against 2.2 ms
+  // for the captured kernel-per-operator graph (its grid barriers and input staging cost what
+  // the launches they replace cost, and its attention stage is slower), and it falls further
+  // behind with more rows.
+  if (EnvFlag("B200_DECODER_STREAM")) {
     s = DecodeStreamCreate(ctx, c, d->layers, embed, final_norm, lm_head,
                            static_cast<int64_t>(c.vocab) * (tp != nullptr ? tp->world : 1), tp, &d->stream_path);
     if (s != B200_OK) {

@@ -205,10 +205,10 @@ def test_silu_mul_and_embed():
 def step_path(request, monkeypatch):
     """Both implementations of the step: the single persistent kernel (taken where the
     shapes and the batch allow it) and the kernel-per-operator graph."""
-    if request.param == "per_op":
-        monkeypatch.setenv("B200_DECODER_NO_STREAM", "1")
+    if request.param == "stream":
+        monkeypatch.setenv("B200_DECODER_STREAM", "1")
     else:
-        monkeypatch.delenv("B200_DECODER_NO_STREAM", raising=False)
+        monkeypatch.delenv("B200_DECODER_STREAM", raising=False)
     return request.param
 
 
@@ -274,9 +274,10 @@ def test_decoder_step_small(batch, step_path):
     (dict(layers=2, hidden=256, heads=2, kv_heads=2, head_dim=128, inter=512, vocab=512), 4, 0, 16),         # G = 1, pos 0
     (dict(layers=2, hidden=256, heads=4, kv_heads=4, head_dim=64, inter=256, vocab=528), 2, 1100, 1104),     # long chunks
 ])
-def test_decoder_stream_shapes(cfgkw, batch, ctx, max_len):
+def test_decoder_stream_shapes(cfgkw, batch, ctx, max_len, monkeypatch):
     """The single-kernel step over the head-group / head-dim variants it is compiled for,
     input widths that are no multiple of a record, the first position and long caches."""
+    monkeypatch.setenv("B200_DECODER_STREAM", "1")
     cfg = inputs.decoder_config(**cfgkw)
     results, dcache, ocache, dec = _run_decoder(cfg, batch, ctx=ctx, max_len=max_len, steps=2)
     assert dec.launches_per_step(batch) == 1
@@ -337,7 +338,7 @@ def test_fresh_tensors_every_step_do_not_grow_the_graph_cache(monkeypatch):
     logits tensor: tokens and position are staged, graphs are keyed by the output pointer and
     the cache is bounded."""
     import torch
-    monkeypatch.setenv("B200_DECODER_NO_STREAM", "1")
+    monkeypatch.delenv("B200_DECODER_STREAM", raising=False)
     cfg = inputs.decoder_config(layers=2, hidden=128, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=512)
     p = pkg()
     params, cache, tokens = inputs.config5(cfg, 2, 3, max_len=128)
