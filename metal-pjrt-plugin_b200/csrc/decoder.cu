@@ -91,6 +91,7 @@ struct b200_decoder {
   b200_tp* tp = nullptr;
   // activations (device, sized for max_batch)
   __nv_bfloat16 *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr;
+  __nv_bfloat16* x2 = nullptr;   // second residual buffer of the push exchange (one CTA writes the new rows while all read the old)
   float *y32 = nullptr, *attn_scratch = nullptr, *logits_local = nullptr, *inv_freq = nullptr;
   __nv_bfloat16* logits_bf16 = nullptr;   // LM head output of the tensor-core route (batches above 8)
   bool use_graph = true;
@@ -112,7 +113,7 @@ namespace {
 
 b200_status Qmm(b200_decoder* d, cudaStream_t stream, const b200_qweight& w, const void* x, void* out, int batch,
                 int64_t N, int64_t K, int epilogue, const void* residual, int prologue = B200_QMM_PRO_NONE,
-                const void* gain = nullptr) {
+                const void* gain = nullptr, const QmmTp* tp = nullptr) {
   b200_qmm_params p = {};
   p.prologue = prologue;
   p.prologue_gain = gain;
@@ -130,7 +131,7 @@ b200_status Qmm(b200_decoder* d, cudaStream_t stream, const b200_qweight& w, con
   p.M = batch;
   p.N = N;
   p.K = K;
-  return b200_qmm_run(d->ctx, stream, &p);
+  return QmmRunEx(d->ctx, stream, &p, tp);
 }
 
 b200_status ResidualNorm(b200_decoder* d, cudaStream_t stream, const void* gain, int batch) {
@@ -164,15 +165,49 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   const bool tp = d->tp != nullptr && d->tp->world > 1;
   const bool peer = tp && d->tp->peer && static_cast<int64_t>(batch) * E <= d->tp->cap;
 
+  // Push exchange (up to 8 rows, peers connected): the o / down projections store their f32
+  // partial sums into every rank's exchange block from their epilogue, and the projection
+  // after them sums the ranks' sub-slots from its own memory, adds the residual and
+  // applies the RMSNorm while it stages its input: no kernel of its own for the exchange.
+  QmmTp link;
+  const bool push = peer && batch <= 8 && !EnvFlag("B200_TP_PULL") && TpPushLink(d->tp, &link);
   // Up to 8 rows the RMSNorm in front of a projection is fused into its input
   // staging (h is never written); beyond that it is its own kernel.
-  const bool fuse_norm = batch <= 8 && !tp;
+  const bool fuse_norm = batch <= 8 && (!tp || push);
+  __nv_bfloat16* xb[2] = {d->x, d->x2};
+  int xp = 0;   // which of the two holds the current residual rows (push exchange)
+  QmmTp from_peers = link, to_peers = link;
+  to_peers.push = true;
+  to_peers.src = nullptr;
   B200_TRY(b200_embed(ctx, stream, d->embed, tokens, d->x, batch, E,
                       static_cast<int64_t>(c.vocab) * (d->tp != nullptr ? d->tp->world : 1)));
   if (!fuse_norm)
     B200_TRY(b200_rownorm(ctx, stream, 0, d->x, d->layers[0].attn_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
   for (int li = 0; li < c.layers; ++li) {
     const b200_decoder_layer& L = d->layers[li];
+    if (push) {
+      if (li == 0) {
+        B200_TRY(Qmm(d, stream, L.qkv, xb[xp], d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM,
+                     L.attn_norm));
+      } else {   // the down projection of the layer before pushed its partial sums
+        from_peers.x_out = xb[xp ^ 1];
+        B200_TRY(Qmm(d, stream, L.qkv, xb[xp], d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM,
+                     L.attn_norm, &from_peers));
+        xp ^= 1;
+      }
+      B200_TRY(b200_attention_step(ctx, stream, d->qkv, L.q_norm, L.k_norm, d->inv_freq, L.k_cache, L.v_cache, d->attn,
+                                   pos, d->attn_scratch, batch, c.heads, c.kv_heads, c.head_dim, c.max_len,
+                                   c.rope_theta, c.rms_eps));
+      B200_TRY(Qmm(d, stream, L.o, d->attn, link.dst[link.rank], batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr,
+                   B200_QMM_PRO_NONE, nullptr, &to_peers));
+      from_peers.x_out = xb[xp ^ 1];
+      B200_TRY(Qmm(d, stream, L.gate_up, xb[xp], d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
+                   nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm, &from_peers));
+      xp ^= 1;
+      B200_TRY(Qmm(d, stream, L.down, d->gu, link.dst[link.rank], batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr,
+                   B200_QMM_PRO_SILU_MUL, nullptr, &to_peers));
+      continue;
+    }
     if (fuse_norm)
       B200_TRY(Qmm(d, stream, L.qkv, d->x, d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM,
                    L.attn_norm));
@@ -255,7 +290,7 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
     b200_qmm_params p = {};
     p.bits = 16;
     p.epilogue = B200_QMM_OUT_F32;
-    p.x = fuse_norm ? d->x : d->h;
+    p.x = push ? xb[xp] : (fuse_norm ? d->x : d->h);
     if (fuse_norm) {
       p.prologue = B200_QMM_PRO_RMSNORM;
       p.prologue_gain = d->final_norm;
@@ -266,7 +301,8 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
     p.M = batch;
     p.N = c.vocab;
     p.K = E;
-    B200_TRY(b200_qmm_run(ctx, stream, &p));
+    from_peers.x_out = nullptr;   // the last down projection's partial sums; nobody needs the residual rows afterwards
+    B200_TRY(QmmRunEx(ctx, stream, &p, push ? &from_peers : nullptr));
   }
   if (tp) B200_TRY(TpAllGather(d->tp, stream, d->logits_local, logits, static_cast<int64_t>(batch) * c.vocab, B200_F32));
   return B200_OK;
@@ -309,6 +345,7 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
   const size_t B = c.max_batch;
   const size_t qkv = static_cast<size_t>(c.heads + 2 * c.kv_heads) * c.head_dim;
   cudaError_t e = Alloc(&d->x, B * c.hidden);
+  if (e == cudaSuccess) e = Alloc(&d->x2, B * c.hidden);
   if (e == cudaSuccess) e = Alloc(&d->h, B * c.hidden);
   if (e == cudaSuccess) e = Alloc(&d->qkv, B * qkv);
   if (e == cudaSuccess) e = Alloc(&d->attn, B * c.heads * c.head_dim);
@@ -361,7 +398,7 @@ void b200_decoder_destroy(b200_decoder* d) {
                   static_cast<void*>(d->attn), static_cast<void*>(d->gu),
                   static_cast<void*>(d->y32), static_cast<void*>(d->attn_scratch),
                   static_cast<void*>(d->logits_local), static_cast<void*>(d->inv_freq),
-                  static_cast<void*>(d->logits_bf16), static_cast<void*>(d->tokens_buf),
+                  static_cast<void*>(d->logits_bf16), static_cast<void*>(d->x2), static_cast<void*>(d->tokens_buf),
                   static_cast<void*>(d->pos_buf)})
     if (p != nullptr) cudaFree(p);
   delete d;

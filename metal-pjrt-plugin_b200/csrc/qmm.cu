@@ -29,7 +29,7 @@
 #include <map>
 #include <utility>
 
-#include "common.cuh"
+#include "tp.cuh"
 
 namespace cg = cooperative_groups;
 using namespace b200;
@@ -94,9 +94,29 @@ struct QmmArgs {
   int tiles;                   // row tiles in all (ceil(N / (16 RT)))
   float eps;
   const __nv_bfloat16* gain;   // RMSNorm gain [K]
+  // tensor-parallel exchange (tp_world == 0: none), see b200::QmmTp
+  int tp_world, tp_rank;
+  float* tp_dst[kTpMaxWorld];            // epilogue kEpiloguePush: slot 0 of this rank's sub-slot on every rank
+  uint32_t* tp_peer_flags[kTpMaxWorld];  // ... and the flag arrays to raise there
+  uint32_t* tp_count;                    // exchanges this rank has pushed (device memory)
+  uint32_t* tp_done;                     // CTAs of the pushing kernel that have finished
+  const float* tp_src;                   // prologue: slot 0 of the partials in this rank's memory, [world][cap]
+  const uint32_t* tp_flags;              // ... and the flags the peers raise here
+  long long tp_cap;                      // floats per sub-slot; a slot is world sub-slots
+  __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
 };
 
 constexpr int kEpilogueGemm = 100;
+constexpr int kEpiloguePush = 101;   // f32 partial sums stored into every rank's exchange block
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t d;
@@ -216,6 +236,14 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
   }
   const float y = bf16_round(v);
   const size_t o = static_cast<size_t>(m) * a.ldo + n;
+  if (a.epilogue == kEpiloguePush) {
+    // plain stores into every rank's memory (its own included); the slot alternates with the exchange number
+    const size_t so_ = static_cast<size_t>((*a.tp_count + 1u) & 1u) * a.tp_world * a.tp_cap + o;
+#pragma unroll
+    for (int r = 0; r < kTpMaxWorld; ++r)
+      if (r < a.tp_world) a.tp_dst[r][so_] = v;
+    return;
+  }
   if (a.epilogue == B200_QMM_OUT_F32_RAW) {
     reinterpret_cast<float*>(a.out)[o] = v;
   } else if (a.epilogue == B200_QMM_OUT_F32) {
@@ -395,6 +423,52 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     scale_load(static_cast<int>(blockIdx.x) * R);
     scale_store(static_cast<int>(blockIdx.x) * R, so);
     pdl_wait();  // x (and the residual) come from the previous kernel
+    // Tensor parallel: x is the old residual; the new one is x + bf16(sum over ranks of the partial
+    // sums that the K-sharded projection before this one pushed into every rank's memory).  That
+    // kernel has finished on this rank (the wait above), so the exchange number is final; the
+    // peers' flags say when their partials have landed here.  After a wait that gave up nothing of
+    // a peer is touched (the sums only ever read this rank's own memory) and the status word says so.
+    const float* tp_slot = nullptr;
+    if (a.tp_src != nullptr) {
+      const uint32_t n = *a.tp_count;
+      tp_slot = a.tp_src + static_cast<size_t>(n & 1u) * a.tp_world * a.tp_cap;
+      if (tid < a.tp_world && tid != a.tp_rank) {
+        bool ok = false;
+        const long long t0 = clock64();
+        for (;;) {
+#pragma unroll 1
+          for (int i = 0; i < 64 && !ok; ++i) ok = static_cast<int32_t>(ld_acquire_sys_u32(a.tp_flags + tid) - n) >= 0;
+          if (ok || clock64() - t0 > 4000000000ll) break;
+        }
+        if (!ok) report_timeout(a.status, 400 + tid);
+      }
+      consumer_barrier();
+    }
+    // eight values of row m starting at k, the partial sums folded in
+    auto load_x8 = [&](int m, int k, float* dst) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(m) * a.ldx + k));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        dst[2 * j] = bf16_lo(w[j]);
+        dst[2 * j + 1] = bf16_hi(w[j]);
+      }
+      if (tp_slot != nullptr) {
+        float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        const float* base = tp_slot + static_cast<size_t>(m) * a.K + k;
+#pragma unroll
+        for (int r = 0; r < kTpMaxWorld; ++r) {   // rank order on every rank: identical sums everywhere
+          if (r < a.tp_world) {
+            const float4 p0 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(r) * a.tp_cap));
+            const float4 p1 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(r) * a.tp_cap) + 1);
+            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
+            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j] = bf16_round(dst[j] + bf16_round(sum[j]));
+      }
+    };
     // RMSNorm in one pass: when every thread stages at most one 16-input unit of a whole row
     // (M * K <= 8192) and warps do not straddle rows, the sum of squares comes from the
     // values the threads hold for staging anyway (one trip to L2, one barrier).
@@ -409,7 +483,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         ss[m] = 0.0f;
         if (m < a.M) {
           const __nv_bfloat16* xr = a.x + static_cast<size_t>(m) * a.ldx;
-          if (x_vec) {
+          if (x_vec && tp_slot != nullptr) {
+            for (int i = tid * 8; i < a.K; i += kConsumerThreads * 8) {
+              float e8[8];
+              load_x8(m, i, e8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) ss[m] = fmaf(e8[j], e8[j], ss[m]);
+            }
+          } else if (x_vec) {
             for (int i = tid * 8; i < a.K; i += kConsumerThreads * 8) {
               const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr + i));
               const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -469,7 +550,17 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             }
           };
         const __nv_bfloat16* xr = a.x + static_cast<size_t>(valid ? um : 0) * a.ldx;
-        if (valid) {
+        if (valid && tp_slot != nullptr) {
+          load_x8(um, kbase + run0, e);
+          load_x8(um, kbase + run1, e + 8);
+          if (blockIdx.x == 0 && a.x_out != nullptr) {   // the new residual row, once (each K slice by its CTA of tile 0)
+            __nv_bfloat16* xo = a.x_out + static_cast<size_t>(um) * a.K + kbase;
+            *reinterpret_cast<uint4*>(xo + run0) = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+            *reinterpret_cast<uint4*>(xo + run1) = make_uint4(pack_bf16(e[8], e[9]), pack_bf16(e[10], e[11]), pack_bf16(e[12], e[13]), pack_bf16(e[14], e[15]));
+          }
+          load_run(a.gain, kbase + run0, gn);
+          load_run(a.gain, kbase + run1, gn + 8);
+        } else if (valid) {
           load_run(xr, kbase + run0, e);
           load_run(xr, kbase + run1, e + 8);
           if (a.prologue == B200_QMM_PRO_RMSNORM) {
@@ -874,6 +965,22 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       cluster_arrive(n_my);
       cluster_wait(n_my);
     }
+    if (a.epilogue == kEpiloguePush) {
+      // The last CTA of this rank to finish closes the exchange: it counts it and raises this
+      // rank's flag on every peer.  (Every CTA read the old count before it got here.)
+      consumer_barrier();
+      if (tid == 0) {
+        const uint32_t n = *a.tp_count + 1u;
+        __threadfence_system();   // this CTA's stores into the peers, before it is counted as finished
+        if (atomicAdd(a.tp_done, 1u) == gridDim.x * gridDim.y - 1u) {
+          *a.tp_done = 0u;
+          *a.tp_count = n;
+          __threadfence_system();
+          for (int r = 0; r < a.tp_world; ++r)
+            if (r != a.tp_rank) st_release_sys_u32(a.tp_peer_flags[r] + a.tp_rank, n);
+        }
+      }
+    }
   }
 }
 
@@ -1127,7 +1234,7 @@ b200_status RunFewRowNT(b200_context* ctx, cudaStream_t stream, const void* mat,
   a.out_f32 = out_f32;
   a.gemm_bias = bias;
   a.aux = aux;
-  a.tiles = pl.tiles;
+  a.tiles = pl.tiles;   // (a = {}: no tensor-parallel exchange)
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e = LaunchFmt<kBf16, false>(pl, a, grid, stream);
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "few-row GEMM launch: %s", cudaGetErrorString(e)));
@@ -1153,6 +1260,14 @@ b200_status b200_qmm_plan(const b200_qmm_params* p, int* rows_per_cta, int* spli
 }
 
 b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_params* p) {
+  return b200::QmmRunEx(ctx, stream, p, nullptr);
+}
+
+}  // extern "C"
+
+namespace b200 {
+
+b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_params* p, const QmmTp* tp) {
   b200_status s = BeginLaunch(ctx);
   if (s != B200_OK) return s;
   s = Validate(p);
@@ -1190,6 +1305,41 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   a.gemm_bias = nullptr;
   a.aux = nullptr;
   a.tiles = pl.tiles;
+  a.tp_world = 0;
+  a.tp_rank = 0;
+  a.tp_count = a.tp_done = nullptr;
+  a.tp_src = nullptr;
+  a.tp_flags = nullptr;
+  a.tp_cap = 0;
+  a.x_out = nullptr;
+  for (int r = 0; r < kTpMaxWorld; ++r) {
+    a.tp_dst[r] = nullptr;
+    a.tp_peer_flags[r] = nullptr;
+  }
+  if (tp != nullptr && tp->world > 1) {
+    if (tp->push && tp->src != nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: a projection either pushes partial sums or consumes them");
+    if (p->M * p->N > tp->cap && tp->push) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: partial sums exceed the exchange block");
+    a.tp_world = tp->world;
+    a.tp_rank = tp->rank;
+    a.tp_cap = tp->cap;
+    a.tp_count = tp->count;
+    if (tp->push) {
+      if (p->epilogue != B200_QMM_OUT_F32_RAW || a.ldo != a.N)
+        return Fail(B200_INVALID_ARGUMENT, "b200_qmm: pushed partial sums are dense raw f32");
+      a.epilogue = kEpiloguePush;
+      a.tp_done = tp->done;
+      for (int r = 0; r < tp->world; ++r) {
+        a.tp_dst[r] = tp->dst[r];
+        a.tp_peer_flags[r] = tp->peer_flags[r];
+      }
+    } else if (tp->src != nullptr) {
+      if (p->prologue != B200_QMM_PRO_RMSNORM || !a.x_vec || a.ldx != a.K || a.K % 8 != 0 || p->M * p->K > tp->cap)
+        return Fail(B200_INVALID_ARGUMENT, "b200_qmm: summing the ranks' partial sums goes with the RMSNorm prologue on dense, aligned rows");
+      a.tp_src = tp->src;
+      a.tp_flags = tp->flags;
+      a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
+    }
+  }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);
   cudaError_t e;
   switch (pl.fmt) {
@@ -1203,6 +1353,10 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
   if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "b200_qmm launch: %s", cudaGetErrorString(e)));
   return EndLaunch(ctx, "b200_qmm");
 }
+
+}  // namespace b200
+
+extern "C" {
 
 b200_status b200_qmm(b200_context* ctx, b200_stream stream, int bits, int group, int nibble_order, const void* x,
                      const void* q, const void* scale, const void* bias_or_null, void* out, int64_t M, int64_t N,

@@ -101,9 +101,11 @@ __global__ void __launch_bounds__(1024) peer_sum_residual_norm_kernel(const Peer
   extern __shared__ float row[];
   __shared__ float scratch[32];
   __shared__ uint32_t seq_s;
+  __shared__ int gave_up;
   pdl_wait();   // this rank's partial comes from the kernel before
   pdl_launch_dependents();
   const int tid = threadIdx.x;
+  if (tid == 0) gave_up = 0;
   if (tid == 0) seq_s = ld_acquire_sys(a.seq) + 1u;   // the number of this exchange
   __syncthreads();
   const uint32_t seq = seq_s;
@@ -122,9 +124,15 @@ __global__ void __launch_bounds__(1024) peer_sum_residual_norm_kernel(const Peer
       for (int i = 0; i < 256 && !ok; ++i) ok = static_cast<int32_t>(ld_acquire_sys(f) - seq) >= 0;
       if (ok || clock64() - t0 > 4000000000ll) break;
     }
-    if (!ok) report_timeout(a.status, 400 + tid);   // the sum below is then wrong; the status says so
+    if (!ok) {
+      report_timeout(a.status, 400 + tid);
+      gave_up = 1;
+    }
   }
   __syncthreads();
+  // A peer that did not answer may be gone, and its memory with it: after a wait that ran out
+  // nothing of any peer is read and nothing is written; the status word tells the host.
+  if (gave_up) return;
   const int64_t base = static_cast<int64_t>(blockIdx.x) * a.n;
   float ss = 0.0f;
   for (int i = tid * 4; i < a.n; i += blockDim.x * 4) {
@@ -175,8 +183,14 @@ __global__ void __launch_bounds__(1024) peer_sum_residual_norm_kernel(const Peer
   }
 }
 
-size_t BlockBytes(int64_t cap) { return static_cast<size_t>(2 * cap) * sizeof(float) + (kTpMaxWorld + 2) * sizeof(uint32_t); }
-uint32_t* FlagsOf(void* block, int64_t cap) { return reinterpret_cast<uint32_t*>(static_cast<float*>(block) + 2 * cap); }
+size_t BlockBytes(int64_t cap, int world) {
+  return static_cast<size_t>(2 + 2 * world) * cap * sizeof(float) + 2 * (kTpMaxWorld + 2) * sizeof(uint32_t);
+}
+float* PushedOf(void* block, int64_t cap) { return static_cast<float*>(block) + 2 * cap; }
+uint32_t* FlagsOf(void* block, int64_t cap, int world) {
+  return reinterpret_cast<uint32_t*>(static_cast<float*>(block) + static_cast<size_t>(2 + 2 * world) * cap);
+}
+uint32_t* PushFlagsOf(void* block, int64_t cap, int world) { return FlagsOf(block, cap, world) + kTpMaxWorld + 2; }
 
 }  // namespace
 
@@ -210,6 +224,24 @@ b200_status TpAllGather(b200_tp* tp, cudaStream_t stream, const void* send, void
   return B200_OK;
 }
 
+bool TpPushLink(b200_tp* tp, QmmTp* out) {
+  if (tp == nullptr || !tp->peer || out == nullptr) return false;
+  *out = QmmTp();
+  out->world = tp->world;
+  out->rank = tp->rank;
+  out->cap = tp->cap;
+  uint32_t* pf = PushFlagsOf(tp->block, tp->cap, tp->world);
+  out->count = pf + kTpMaxWorld;
+  out->done = pf + kTpMaxWorld + 1;
+  out->src = PushedOf(tp->block, tp->cap);
+  out->flags = pf;
+  for (int r = 0; r < tp->world; ++r) {
+    out->dst[r] = PushedOf(tp->peer_block[r], tp->cap) + static_cast<int64_t>(tp->rank) * tp->cap;
+    out->peer_flags[r] = PushFlagsOf(tp->peer_block[r], tp->cap, tp->world);
+  }
+  return true;
+}
+
 float* TpPeerPartial(b200_tp* tp, int slot) {
   if (tp == nullptr || !tp->peer || slot < 0 || slot > 1) return nullptr;
   return static_cast<float*>(tp->block) + static_cast<int64_t>(slot) * tp->cap;
@@ -228,9 +260,9 @@ b200_status TpSumResidualNorm(b200_tp* tp, cudaStream_t stream, int slot, void* 
   PeerArgs a = {};
   for (int r = 0; r < tp->world; ++r) {
     a.partial[r] = static_cast<const float*>(tp->peer_block[r]) + static_cast<int64_t>(slot) * tp->cap;
-    a.peer_flags[r] = FlagsOf(tp->peer_block[r], tp->cap);
+    a.peer_flags[r] = FlagsOf(tp->peer_block[r], tp->cap, tp->world);
   }
-  a.flags = FlagsOf(tp->block, tp->cap);
+  a.flags = FlagsOf(tp->block, tp->cap, tp->world);
   a.seq = a.flags + kTpMaxWorld;
   a.done = a.flags + kTpMaxWorld + 1;
   a.rank = tp->rank;
@@ -269,8 +301,8 @@ b200_status b200_tp_peer_alloc(b200_tp* tp, int64_t max_floats, void* handle_out
                 static_cast<long long>(max_floats), tp->world, kTpMaxWorld);
   const int64_t cap = (max_floats + 3) / 4 * 4;
   void* block = nullptr;
-  cudaError_t e = cudaMalloc(&block, BlockBytes(cap));
-  if (e == cudaSuccess) e = cudaMemset(block, 0, BlockBytes(cap));
+  cudaError_t e = cudaMalloc(&block, BlockBytes(cap, tp->world));
+  if (e == cudaSuccess) e = cudaMemset(block, 0, BlockBytes(cap, tp->world));
   cudaIpcMemHandle_t h;
   if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, block);
   if (e != cudaSuccess) {

@@ -12,8 +12,12 @@ from util import ROOT
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, out_q, peers):
+def _worker(rank, world, port, out_q, peers, hidden, B):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    if peers == "pull":   # the separate exchange kernel instead of the push from the projections' epilogue
+        os.environ["B200_TP_PULL"] = "1"
+    else:
+        os.environ.pop("B200_TP_PULL", None)
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch
@@ -28,10 +32,10 @@ def _worker(rank, world, port, out_q, peers):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     ctx = pkg.Context(rank)
     tp = parallel.TensorParallel.from_torch_distributed(ctx)
-    if peers:   # the sums over ranks as one kernel over peer memory instead of NCCL
-        tp.connect_peers(4 * 256)
-    cfg = inputs.decoder_config(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=512, vocab=1024)
-    B, ctxlen, max_len = 3, 40, 64
+    if peers:   # the sums over ranks over peer memory instead of NCCL
+        tp.connect_peers(4 * hidden)
+    cfg = inputs.decoder_config(layers=3, hidden=hidden, heads=4, kv_heads=2, head_dim=64, inter=2 * hidden, vocab=1024)
+    ctxlen, max_len = 40, 64
     params, cache, tokens = inputs.config5(cfg, B, ctxlen, max_len=max_len)
     sp, sc, local = parallel.shard_params(params, cache, cfg, rank, world)
     device = f"cuda:{rank}"
@@ -61,16 +65,20 @@ def _worker(rank, world, port, out_q, peers):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("peers", [False, True])
-def test_tp2_decoder_matches_oracle(peers):
+@pytest.mark.parametrize("peers,hidden,B", [(False, 256, 3), ("pull", 256, 3), ("push", 256, 3), ("push", 512, 1),
+                                            ("push", 512, 2), ("push", 256, 8)])
+def test_tp2_decoder_matches_oracle(peers, hidden, B):
+    """Sums over ranks by NCCL, by the exchange kernel that pulls the peers' partial sums, and by
+    the projections pushing theirs (the two RMSNorm staging variants of the consuming
+    projection: rows that fit one pass, and the two-pass form)."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000 + (7 if peers else 0)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peers)) for r in range(2)]
+    port = 29500 + os.getpid() % 2000 + {False: 0, "pull": 7, "push": 13}[peers] + hidden // 64 + B
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peers, hidden, B)) for r in range(2)]
     for p_ in procs:
         p_.start()
     res = dict(q.get(timeout=300) for _ in range(2))
@@ -79,4 +87,5 @@ def test_tp2_decoder_matches_oracle(peers):
         assert p_.exitcode == 0
     err, same_argmax, replay_equal, status = res[0]
     assert status == 0
+    print(f"tp2 {peers} hidden {hidden} batch {B}: max logit error {err:.3e} x RMS")
     assert err <= 6e-2 and same_argmax and replay_equal
