@@ -234,28 +234,37 @@ def build_device_model(pkg, cfg_local, batch, device, seed, world, rank, ctx):
 
 
 def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
-    """The dequant-GEMV alone: every int4 projection of the model launched back
-    to back over its own weights (4 x layers distinct buffers, far beyond L2)."""
+    """The dequant-GEMV alone, in the forms the decode step launches it: every int4
+    projection of the model back to back over its own weights (4 x layers distinct buffers,
+    far beyond L2), qkv and gate_up with the fused RMSNorm staging, o with the residual
+    epilogue, down with the fused silu(gate) * up staging and the residual epilogue."""
     import torch
     E, H, KV, D, I = (cfg_local[k] for k in ("hidden", "heads", "kv_heads", "head_dim", "inter"))
-    xs = {E: torch.randn((batch, E), device=device).to(torch.bfloat16),
-          H * D: torch.randn((batch, H * D), device=device).to(torch.bfloat16),
-          I: torch.randn((batch, I), device=device).to(torch.bfloat16)}
+    bf = torch.bfloat16
+    x_e = torch.randn((batch, E), device=device).to(bf)
+    x_hd = torch.randn((batch, H * D), device=device).to(bf)
+    x_gu = torch.randn((batch, 2 * I), device=device).to(bf)
+    res = torch.randn((batch, E), device=device).to(bf)
+    gain = torch.ones((E,), device=device, dtype=bf)
+    forms = {"qkv": lambda w: pkg.qwen3.linear(x_e, w, rms_gain=gain, ctx=ctx),
+             "o": lambda w: pkg.qwen3.linear(x_hd, w, residual=res, ctx=ctx),
+             "gate_up": lambda w: pkg.qwen3.linear(x_e, w, rms_gain=gain, ctx=ctx),
+             "down": lambda w: pkg.qwen3.linear(x_gu, w, silu_mul=True, residual=res, ctx=ctx)}
     jobs, nbytes = [], 0
     for lp in params["layers"]:
         for name in ("qkv", "o", "gate_up", "down"):
             w = lp[name]
             n, k = w["q4"].shape[0], w["q4"].shape[1] * 8
-            jobs.append((xs[k], w))
+            jobs.append((forms[name], w))
             nbytes += n * k * 0.5625 + 2 * batch * (k + n)
-    for x, w in jobs[:8]:
-        pkg.qwen3.linear(x, w, ctx=ctx)
+    for f, w in jobs[:8]:
+        f(w)
     torch.cuda.synchronize()
     # one CUDA graph of all the launches, so the figure is device time and not the host's launch rate
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        for x, w in jobs:
-            pkg.qwen3.linear(x, w, ctx=ctx)
+        for f, w in jobs:
+            f(w)
     graph.replay()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -267,6 +276,80 @@ def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
     ms = start.elapsed_time(stop)
     launches = reps * len(jobs)
     return nbytes / len(jobs), ms * 1e-3 / launches, launches
+
+
+def stand_alone_ops(pkg, quick):
+    """The stand-alone operators of the C ABI: CUDA-event times of CUDA-graph replays over
+    buffers rotated beyond L2 (opbench.py).  quick: fewer repetitions and shapes."""
+    import opbench
+    out = {}
+    reps = 2 if quick else 4
+    shapes = {"qkv": (4096, 6144), "o": (4096, 4096), "gate_up": (4096, 24576), "down": (12288, 4096)}
+    for bits, tag in ((4, "int4_g64"), (8, "int8_per_channel")):
+        for name, (k, n) in shapes.items():
+            nb = max(8, min(48, int(400e6 // (n * k * bits / 8))))
+            r = opbench.bench_qmm(pkg, bits, 1, n, k, nb, reps, 64 if bits == 4 else 0)
+            out[f"qgemv_{tag}_m1_{name}"] = {"us": round(r["us"], 2), "gbs": round(r["gbs"], 1)}
+    for m in ((1, 2048, 8192) if quick else (1, 16, 128, 2048, 8192)):   # configs[1]: bf16, bias + SiLU, K = N = 4096
+        r = opbench.bench_gemm(pkg, m, 4096, 4096, 3, True, reps)
+        out[f"gemm_bf16_bias_silu_m{m}"] = {"us": round(r["us"], 2), "tflops": round(r["tflops"], 1), "gbs": round(r["gbs"], 1),
+                                            "route": r["route"]}
+    for kind, rows, n, dt in (("softmax", 8192, 1024, "f32"), ("layernorm", 8192, 1024, "f32"), ("rms", 8192, 4096, "bf16")):
+        r = opbench.bench_rows(pkg, kind, rows, n, dt, reps)
+        out[f"rownorm_{kind}_{rows}x{n}_{dt}"] = {"us": round(r["us"], 2), "gbs": round(r["gbs"], 1)}
+    # configs[0]: f32 x[512,1024] @ W[1024,1024] + b, then RMSNorm
+    import torch
+    x = torch.randn((512, 1024), device="cuda")
+    w = torch.randn((1024, 1024), device="cuda") / 32
+    b = torch.randn((1024,), device="cuda") * 0.01
+    gain = torch.ones((1024,), device="cuda")
+    y = torch.empty((512, 1024), device="cuda")
+    B = pkg.blas
+    prm = B.GemmParams(512, 1024, 1024, B.Operand(x, 1024), B.Operand(w, 1024), B.Operand(y, 1024))
+    epi = B.SteelEpilogue(0, b)
+
+    def block():
+        B.run_steel_gemm(prm, epi)
+        pkg.rows.rownorm(0, y, gain=gain, eps=1e-6, out=y)
+    out["config0_f32_gemm_bias_rmsnorm_512x1024x1024"] = {"us": round(opbench.timed(block, 20) * 1e6, 2)}
+    return out
+
+
+def parity_check(pkg, ctx, tp, world, rank, device):
+    """One step of a small decoder (sharded like the benchmarked one when world > 1) against
+    the NumPy oracle on rank 0; outside every timed region."""
+    import torch
+    from oracle import decoder as odec
+    from oracle import inputs
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from util import dev, dev_params, host
+    cfg = inputs.decoder_config(layers=2, hidden=512, heads=8, kv_heads=8, head_dim=64, inter=1024, vocab=2048)
+    B, ctxlen, max_len = 1, 40, 64
+    params, cache, tokens = inputs.config5(cfg, B, ctxlen, max_len=max_len)
+    local = cfg
+    sp, sc = params, cache
+    if world > 1:
+        from metal_pjrt_plugin_b200 import parallel
+        sp, sc, local = parallel.shard_params(params, cache, cfg, rank, world)
+    dec = pkg.qwen3.Decoder(dev_params(sp, device), {k: [dev(a, device) for a in v] for k, v in sc.items()}, local,
+                            max_batch=B, ctx=ctx, tp=tp)
+    logits = dec.step(dev(tokens.astype(np.int32), device), torch.tensor([ctxlen], dtype=torch.int32, device=device))
+    torch.cuda.synchronize()
+    got = host(logits)
+    if world > 1:
+        got = np.concatenate([got[r] for r in range(world)], axis=-1)
+    res = None
+    if rank == 0:
+        want = odec.decode_step(params, tokens, {k: [a.copy() for a in v] for k, v in cache.items()}, ctxlen, cfg)
+        rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        res = {"workload": "2-layer decoder (hidden 512, 8 heads x 64, inter 1024, vocab 2048), one step at pos 40, "
+                           f"{'sharded over %d ranks' % world if world > 1 else 'one GPU'}, against the NumPy oracle",
+               "err_over_rms": float(np.max(np.abs(got.astype(np.float64) - want)) / rms),
+               "argmax_equal": bool(np.array_equal(got.argmax(-1), want.argmax(-1))),
+               "tolerance": 2e-2, "launches_per_step": int(dec.launches_per_step(B))}
+        res["ok"] = bool(res["err_over_rms"] <= 2e-2 and res["argmax_equal"])
+    dec.close()
+    return res
 
 
 def run_ours(args):
@@ -354,6 +437,8 @@ def run_ours(args):
     bytes_per_launch, sec_per_launch, qlaunches = time_projection_kernels(pkg, params, cfg_local, B, device, reps=3, ctx=ctx)
     achieved = bytes_per_launch / sec_per_launch / 1e9
 
+    parity = parity_check(pkg, ctx, tp, world, rank, device)
+    ops = stand_alone_ops(pkg, quick=args.quick_ops) if (world == 1 and not args.no_ops) else None
     barrier()   # no rank tears down (and frees its exchange block) while another still runs
     if rank != 0:
         if world > 1:
@@ -374,7 +459,8 @@ def run_ours(args):
         "step_hbm": {"algorithmic_gb_per_step": total_bytes / 1e9,
                      "achieved_gbs_per_gpu": total_bytes / world / (t_dev / args.steps) / 1e9,
                      "frac_of_peak": total_bytes / world / (t_dev / args.steps) / 1e9 / peak},
-        "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (int4-g64 dequant-GEMV, all 4 x layers projections)",
+        "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (int4-g64 dequant-GEMV: all 4 x layers projections as the decode step "
+                                               "launches them, fused RMSNorm / silu(gate)*up staging and residual epilogue included)",
                      "achieved": achieved, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s",
                      "frac": achieved / peak, "frac_of_nominal_8tbs": achieved / 8000.0,
                      "algorithmic_bytes_per_launch": bytes_per_launch, "us_per_launch": sec_per_launch * 1e6,
@@ -382,8 +468,10 @@ def run_ours(args):
                      # DRAM read+write of one launch from the ncu capture of the gate_up shape
                      # (56.76 MB moved for 56.62 MB algorithmic), scaled to this mean launch
                      "traffic": bytes_per_launch * (56.719872 + 0.039936) / 56.623104},
-        "clocks": clk, "device_status": err,
+        "clocks": clk, "device_status": err, "parity": parity,
     }
+    if ops is not None:
+        line["ops"] = ops
     if cb is not None:
         line["cpu_baseline"] = cb
     print(json.dumps(line), flush=True)
@@ -398,6 +486,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the stand-alone operator timings")
+    ap.add_argument("--quick-ops", action="store_true", help="fewer shapes and repetitions in the stand-alone operator timings")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the sums over ranks by the library's peer-memory kernel, or by ncclAllReduce")
     args = ap.parse_args()

@@ -111,6 +111,50 @@ uint64_t b200_gemm_work(const b200_gemm_params* p);
  * steel_gemm.h:72-78): force a route (b200_gemm_route_t), 0 = automatic. */
 void b200_gemm_force_route(b200_context* ctx, int route);
 
+/* ---- the BlasLt front of the dense GEMM ---------------------------------------
+ * What XLA's GEMM thunk hands a plugin, in plain C: operand layouts that may be
+ * column-major, one of twelve fused epilogues, C and D as separate buffers.
+ * b200_matrix_layout ≙ the fields of gpu::MatrixLayout that ValidateMatmul reads,
+ * b200_matmul_config ≙ gpu::GemmConfig (metal_pjrt/blas/blas_lt_support.cc:102-201);
+ * the epilogue codes follow the order of DecodeEpilogue's switch (:25-82), a binder
+ * maps XLA's BlasLt::Epilogue values onto them. */
+typedef enum { B200_ROW_MAJOR = 0, B200_COLUMN_MAJOR = 1 } b200_matrix_order;
+typedef struct {
+  int32_t dtype;               /* b200_dtype */
+  int32_t order;               /* b200_matrix_order */
+  int64_t num_rows, num_cols;  /* of the logical matrix */
+  int64_t leading_dim_stride;  /* elements between consecutive rows (row-major) / columns (column-major) */
+  int64_t batch_size, batch_stride;
+  int32_t transpose;           /* must be 0 (blas_lt_support.cc:112-118) */
+} b200_matrix_layout;
+typedef struct {
+  b200_matrix_layout lhs, rhs, c, out;
+  double alpha_real, alpha_imag, beta;
+} b200_matmul_config;
+typedef enum { B200_EPI_DEFAULT = 0, B200_EPI_RELU, B200_EPI_BIAS, B200_EPI_BIAS_RELU, B200_EPI_GELU, B200_EPI_GELU_AUX,
+               B200_EPI_BIAS_GELU, B200_EPI_BIAS_GELU_AUX, B200_EPI_SILU, B200_EPI_SILU_AUX, B200_EPI_BIAS_SILU,
+               B200_EPI_BIAS_SILU_AUX } b200_blaslt_epilogue;
+typedef struct { int32_t bias, act, aux; } b200_epilogue_spec;   /* ≙ EpilogueSpec, blas_lt_support.h:44-49; act as in b200_epilogue */
+typedef struct {
+  int32_t swap;                /* column-major output: A and B change places, every layout is seen transposed */
+  b200_gemm_params params;     /* row-major normal form; pointers are filled in at execution */
+  b200_epilogue_spec epi;
+} b200_matmul_plan;
+/* ≙ DecodeEpilogue (blas_lt_support.cc:25-82).  Pure. */
+b200_status b200_decode_epilogue(int32_t epilogue, b200_epilogue_spec* out);
+/* ≙ ValidateMatmul + GetMatmulPlan (blas_lt_support.cc:102-201, metal_blas.cc:245-281): the
+ * acceptance rules (one operand type of f32/f16/bf16, result that type or f32; real alpha; no
+ * transpose flags; batch = max of the operands', an operand without batch is broadcast;
+ * beta != 0 needs C laid out exactly like D; the 16-bit index limits) and the normal form.
+ * Unsupported requests fail here, never at execution with wrong values.  Pure. */
+b200_status b200_matmul_plan_create(const b200_matmul_config* cfg, int32_t epilogue, b200_matmul_plan* out);
+/* ≙ MatmulPlan::ExecuteOnStream + EpilogueBuffers (metal_blas.cc:296-378): operands swapped if
+ * planned, D seeded with C when beta != 0 and they are distinct buffers, D / bias / aux sizes
+ * checked (bias holds n elements of D's type, aux has D's extent), empty problems are no-ops. */
+b200_status b200_matmul_execute(b200_context* ctx, b200_stream stream, const b200_matmul_plan* plan, const void* a,
+                                const void* b, const void* c, void* d, const void* bias, void* aux, size_t d_bytes,
+                                size_t bias_bytes, size_t aux_bytes);
+
 /* ---- weight-only quantised matmul ------------------------------------------
  * out[M, N] = x[M, K] . dequant(W)[N, K]^T, W stored [N, K] with K contiguous
  * (the reference keeps [out, in], examples/llm/qwen3.py:102).  The reference has

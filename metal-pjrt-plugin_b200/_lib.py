@@ -43,6 +43,30 @@ class EpilogueC(C.Structure):
     _fields_ = [("act", C.c_int32), ("bias", C.c_void_p), ("aux", C.c_void_p)]
 
 
+class MatrixLayoutC(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("order", C.c_int32), ("num_rows", C.c_int64), ("num_cols", C.c_int64),
+                ("leading_dim_stride", C.c_int64), ("batch_size", C.c_int64), ("batch_stride", C.c_int64),
+                ("transpose", C.c_int32)]
+
+
+class MatmulConfigC(C.Structure):
+    _fields_ = [("lhs", MatrixLayoutC), ("rhs", MatrixLayoutC), ("c", MatrixLayoutC), ("out", MatrixLayoutC),
+                ("alpha_real", C.c_double), ("alpha_imag", C.c_double), ("beta", C.c_double)]
+
+
+class EpilogueSpecC(C.Structure):
+    _fields_ = [("bias", C.c_int32), ("act", C.c_int32), ("aux", C.c_int32)]
+
+
+class MatmulPlanC(C.Structure):
+    _fields_ = [("swap", C.c_int32), ("params", GemmParamsC), ("epi", EpilogueSpecC)]
+
+
+ROW_MAJOR, COLUMN_MAJOR = 0, 1
+(EPI_DEFAULT, EPI_RELU, EPI_BIAS, EPI_BIAS_RELU, EPI_GELU, EPI_GELU_AUX, EPI_BIAS_GELU, EPI_BIAS_GELU_AUX, EPI_SILU,
+ EPI_SILU_AUX, EPI_BIAS_SILU, EPI_BIAS_SILU_AUX) = range(12)
+
+
 class QmmParamsC(C.Structure):
     _fields_ = [("bits", C.c_int32), ("group", C.c_int32), ("nibble_order", C.c_int32),
                 ("epilogue", C.c_int32), ("x", C.c_void_p), ("q", C.c_void_p), ("scale", C.c_void_p),
@@ -82,6 +106,10 @@ PROTOTYPES = {
     "b200_gemm_route": (_I, [C.POINTER(GemmParamsC), C.POINTER(EpilogueC)]),
     "b200_gemm_work": (C.c_uint64, [C.POINTER(GemmParamsC)]),
     "b200_gemm_force_route": (None, [_VP, _I]),
+    "b200_decode_epilogue": (_I, [C.c_int32, C.POINTER(EpilogueSpecC)]),
+    "b200_matmul_plan_create": (_I, [C.POINTER(MatmulConfigC), C.c_int32, C.POINTER(MatmulPlanC)]),
+    "b200_matmul_execute": (_I, [_VP, _VP, C.POINTER(MatmulPlanC), _VP, _VP, _VP, _VP, _VP, _VP, C.c_size_t, C.c_size_t,
+                                 C.c_size_t]),
     "b200_qmm_validate": (_I, [C.POINTER(QmmParamsC)]),
     "b200_qmm_run": (_I, [_VP, _VP, C.POINTER(QmmParamsC)]),
     "b200_qmm": (_I, [_VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP, _VP, _I64, _I64, _I64, _I]),

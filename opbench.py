@@ -3,17 +3,17 @@ bench/gemm_bench.cc:7-16,102-124 and bench/jax_bench.py: back-to-back launches
 cycling through distinct weight buffers so nothing stays in L2; CUDA-event
 time; JSON lines).  Also the small cases the ncu summaries under profiles/ come from.
 
-    python metal-pjrt-plugin_b200/opbench.py qmm  --bits 4 --m 1 --n 4096 --k 4096 [--buffers 32] [--reps 5]
-    python metal-pjrt-plugin_b200/opbench.py gemm --m 2048 --n 4096 --k 4096 [--act 3] [--bias]
-    python metal-pjrt-plugin_b200/opbench.py rows --kind softmax --rows 8192 --n 1024 [--dtype f32]
-    python metal-pjrt-plugin_b200/opbench.py sweep          # the benchmark configs 2-4
+    python opbench.py qmm  --bits 4 --m 1 --n 4096 --k 4096 [--buffers 32] [--reps 5]
+    python opbench.py gemm --m 2048 --n 4096 --k 4096 [--act 3] [--bias]
+    python opbench.py rows --kind softmax --rows 8192 --n 1024 [--dtype f32]
+    python opbench.py sweep          # the benchmark configs 2-4
 """
 import argparse
 import json
 import os
 import sys
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 from __graft_entry__ import load_package  # noqa: E402
 

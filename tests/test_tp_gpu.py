@@ -18,6 +18,7 @@ def _worker(rank, world, port, out_q, peers, hidden, B):
         os.environ["B200_TP_PULL"] = "1"
     else:
         os.environ.pop("B200_TP_PULL", None)
+        os.environ["B200_TP_PUSH_ROWS"] = "8"   # the push at every batch it supports (the default stops at 2 rows)
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch
