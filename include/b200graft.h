@@ -354,6 +354,22 @@ b200_status b200_attention_step(b200_context* ctx, b200_stream stream, const voi
 b200_status b200_silu_mul(b200_context* ctx, b200_stream stream, const void* gate_up, void* out,
                           int64_t batch, int64_t inter);
 
+/* ---- sampling ------------------------------------------------------------------
+ * ≙ sample (examples/llm/qwen3.py:395-418): next token [batch] from f32 logits [batch, vocab].
+ * temperature 0 is greedy (argmax, ties to the lowest index; `uniform` may be NULL).
+ * Otherwise logits / temperature, then: neither top_k nor top_p set - a categorical draw
+ * over the row; else the top_k values in descending order (ties: lower index first), of
+ * which top_p < 1 keeps the smallest prefix whose probability reaches top_p (always at
+ * least the most likely token), and a categorical draw over those.  The draw is the
+ * inverse CDF at uniform[row] in [0, 1) (the reference draws with jax.random.categorical,
+ * whose bit stream only JAX has): the first candidate, in the order above, whose cumulative
+ * probability exceeds uniform[row] x the kept total.
+ * Refused: temperature < 0, top_k outside [0, vocab] (INVALID_ARGUMENT, as the reference
+ * raises); top_k > 1024, and top_p < 1 with top_k == 0 (UNIMPLEMENTED: that sorts the whole
+ * vocabulary). */
+b200_status b200_sample(b200_context* ctx, b200_stream stream, const float* logits, int64_t batch, int64_t vocab,
+                        float temperature, int32_t top_k, float top_p, const float* uniform, int32_t* out);
+
 /* ---- tensor parallel group (NEW: the reference is single-device,
  * metal_pjrt/compiler/metal_collectives_registration.cc:10-17) ------------------
  * One process per GPU.  Rank 0 makes an id, the caller distributes its bytes

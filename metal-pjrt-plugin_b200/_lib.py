@@ -134,6 +134,7 @@ PROTOTYPES = {
     "b200_attention_step": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I64, _I, _I, _I, _I64,
                                  C.c_float, C.c_float]),
     "b200_silu_mul": (_I, [_VP, _VP, _VP, _VP, _I64, _I64]),
+    "b200_sample": (_I, [_VP, _VP, _VP, _I64, _I64, C.c_float, C.c_int32, C.c_float, _VP, _VP]),
     "b200_tp_make_id": (_I, [_VP]),
     "b200_tp_create": (_I, [_VP, _VP, _I, _I, C.POINTER(_VP)]),
     "b200_tp_destroy": (None, [_VP]),

@@ -121,6 +121,19 @@ def qmm_plan(M, N, K, bits=4, group=64):
     return r.value, s.value, m.value
 
 
+def sample(logits, uniform=None, *, temperature=0.0, top_k=0, top_p=1.0, ctx=None, stream=None):
+    """≙ sample (qwen3.py:395-418): next token int32 [B] from f32 logits [B, V] on the device;
+    temperature 0 is greedy.  `uniform` (f32 [B] in [0, 1), device) replaces the reference's
+    PRNG key: the categorical draw is the inverse CDF at that number."""
+    torch = _torch()
+    ctx = ctx or default_context(logits.device.index or 0)
+    B, V = logits.shape
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib().b200_sample(ctx.handle, stream or _lib.current_stream(), _lib.ptr(logits.contiguous()), B, V,
+                                      float(temperature), int(top_k), float(top_p), _lib.ptr(uniform), _lib.ptr(out)))
+    return out
+
+
 def init_cache(cfg, batch, max_len, device="cuda"):
     """≙ init_cache (qwen3.py:279-291): per-layer K [B, KV, S, D] and V [B, KV, D, S]."""
     torch = _torch()
