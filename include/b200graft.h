@@ -63,6 +63,13 @@ b200_status b200_context_error(b200_context* ctx);
  * (1 = next) is refused before it is enqueued and sets the sticky error.
  * n <= 0 disarms. */
 void b200_context_fail_launch_after(b200_context* ctx, int64_t n);
+/* Exercises the path every bounded device-side wait of this library takes when it runs out
+ * (≙ what tests/test_gpu_errors.py:21-65 does for the reference's sticky device error, made
+ * on purpose without faulting anything): enqueues a kernel that waits, for at most
+ * `limit_cycles` SM cycles, on a barrier nobody arrives at, gives up, writes B200_TIMEOUT and
+ * its wait id (900) to the status word and returns.  After the stream is synchronised
+ * b200_context_error turns sticky B200_TIMEOUT; other contexts are unaffected. */
+b200_status b200_context_wait_probe(b200_context* ctx, b200_stream stream, int64_t limit_cycles);
 /* Number of kernels this context has enqueued so far. */
 int64_t b200_context_launch_count(b200_context* ctx);
 
@@ -222,6 +229,19 @@ b200_status b200_dequantize(b200_context* ctx, b200_stream stream, int bits, int
  * with sequential uint32 nibbles.  scale/bias are written as bf16. */
 b200_status b200_quantize(b200_context* ctx, b200_stream stream, int bits, int group, const void* w,
                           int w_dtype, void* q_out, void* scale_out, void* bias_out, int64_t N, int64_t K);
+
+/* The reference's own load-time 4-bit quantiser on the device (≙ quantize_int4,
+ * qwen3.py:169-196: the grid anchored at the group's largest-magnitude edge, stretched so
+ * that zero falls on it, step possibly negative), bit for bit, in the reference's layout:
+ * q uint8 [N, K/64, 32] (low nibble = element j, high nibble = element j + 32), scale and
+ * bias bf16 [N, K/64].  (Its int8 quantiser, qwen3.py:154-166, is b200_quantize with bits 8
+ * and group 64.)  w f32 or bf16 [N, K]. */
+b200_status b200_quantize_int4_ref(b200_context* ctx, b200_stream stream, const void* w, int w_dtype, void* q_out,
+                                   void* scale_out, void* bias_out, int64_t N, int64_t K);
+/* Split-half bytes (nibble_order 1) -> sequential uint32 words (nibble_order 0), the layout
+ * b200_decoder_create takes.  Scale and bias are shared by both layouts. */
+b200_status b200_repack_int4(b200_context* ctx, b200_stream stream, const void* q_split_half, void* q_sequential,
+                             int64_t N, int64_t K);
 
 /* ---- row reductions over the minor dimension --------------------------------
  * kind 0 RMSNorm  y = x * rsqrt(mean(x^2) + eps) * gain   (examples/llm/qwen3.py:294-297)

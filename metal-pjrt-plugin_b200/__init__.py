@@ -11,6 +11,6 @@ and streams; no computation happens in Python and nothing falls back to the CPU.
 from . import _lib
 from ._lib import B200Error, lib
 from .context import Context, default_context
-from . import blas, qwen3, rows
+from . import blas, loader, qwen3, rows
 
-__all__ = ["_lib", "B200Error", "lib", "Context", "default_context", "blas", "qwen3", "rows"]
+__all__ = ["_lib", "B200Error", "lib", "Context", "default_context", "blas", "loader", "qwen3", "rows"]

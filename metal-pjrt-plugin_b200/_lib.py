@@ -101,6 +101,7 @@ PROTOTYPES = {
     "b200_context_error": (_I, [_VP]),
     "b200_context_fail_launch_after": (None, [_VP, _I64]),
     "b200_context_launch_count": (_I64, [_VP]),
+    "b200_context_wait_probe": (_I, [_VP, _VP, _I64]),
     "b200_gemm_validate": (_I, [C.POINTER(GemmParamsC), C.POINTER(EpilogueC)]),
     "b200_gemm": (_I, [_VP, _VP, C.POINTER(GemmParamsC), C.POINTER(EpilogueC)]),
     "b200_gemm_route": (_I, [C.POINTER(GemmParamsC), C.POINTER(EpilogueC)]),
@@ -116,6 +117,8 @@ PROTOTYPES = {
     "b200_qmm_plan": (_I, [C.POINTER(QmmParamsC), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I)]),
     "b200_dequantize": (_I, [_VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP, _I64, _I64, _I]),
     "b200_quantize": (_I, [_VP, _VP, _I, _I, _VP, _I, _VP, _VP, _VP, _I64, _I64]),
+    "b200_quantize_int4_ref": (_I, [_VP, _VP, _VP, _I, _VP, _VP, _VP, _I64, _I64]),
+    "b200_repack_int4": (_I, [_VP, _VP, _VP, _VP, _I64, _I64]),
     "b200_rownorm": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _VP, _I64, _I64, _I, _D]),
     "b200_decoder_create": (_I, [_VP, C.POINTER(DecoderConfigC), C.POINTER(DecoderLayerC), _VP, _VP, _VP, _VP,
                                  C.POINTER(_VP)]),

@@ -74,9 +74,37 @@ b200_status EndLaunch(b200_context* ctx, const char* what, int kernels) {
 
 using namespace b200;
 
+namespace {
+
+// Waits on an mbarrier that nobody ever arrives at, with the caller's limit, and reports the
+// way every bounded wait of this library reports: first report wins, B200_TIMEOUT and the
+// wait's id in the status word; then it returns normally (no trap, the context stays usable).
+__global__ void wait_probe_kernel(long long limit_cycles, int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    const long long t0 = clock64();
+    bool ok = false;
+    while (!ok && clock64() - t0 <= limit_cycles) ok = mbar_try_wait(&bar, 0);
+    if (!ok) report_timeout(status, 900);
+  }
+}
+
+}  // namespace
+
 extern "C" {
 
 int b200_abi_version(void) { return B200_ABI_VERSION; }
+
+b200_status b200_context_wait_probe(b200_context* ctx, b200_stream stream, int64_t limit_cycles) {
+  b200_status s = BeginLaunch(ctx);
+  if (s != B200_OK) return s;
+  if (limit_cycles < 1 || limit_cycles > 4000000000ll)
+    return Fail(B200_INVALID_ARGUMENT, "b200_context_wait_probe: limit of %lld cycles (1 .. 4e9)", static_cast<long long>(limit_cycles));
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_cycles, ctx->dev_status);
+  return EndLaunch(ctx, "b200_context_wait_probe");
+}
 
 const char* b200_last_error(void) { return g_error; }
 

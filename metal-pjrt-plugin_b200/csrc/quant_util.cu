@@ -76,6 +76,64 @@ __global__ void quantize_int4_kernel(const T* w, uint32_t* q, __nv_bfloat16* sca
   }
 }
 
+// The reference's own 4-bit grid (quantize_int4, examples/llm/qwen3.py:169-196, MLX's affine
+// grid): anchored at the group's largest-magnitude edge and stretched so that zero falls on
+// it; the step may be negative.  Output in the reference's layout: byte j of a group holds
+// element j in its low nibble and element j + 32 in its high nibble.  One warp per (row, group),
+// lane j owns byte j.  Every operation is the IEEE f32 one NumPy performs, so the result is the
+// reference's bit for bit.
+template <typename T>
+__global__ void quantize_int4_ref_kernel(const T* w, uint8_t* q, __nv_bfloat16* scale, __nv_bfloat16* bias, int64_t N,
+                                         int64_t K) {
+  const int lane = threadIdx.x & 31;
+  const int64_t groups = K / 64;
+  const int64_t total = N * groups;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t wg = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5; wg < total; wg += warps) {
+    const int64_t n = wg / groups, g = wg % groups;
+    const int64_t base = n * K + g * 64;
+    const float v0 = ld(w, base + lane), v1 = ld(w, base + lane + 32);
+    float lo = fminf(v0, v1), hi = fmaxf(v0, v1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    const bool neg = fabsf(lo) > fabsf(hi);
+    float s = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-12f), 15.0f);
+    s = neg ? s : -s;
+    const float edge = neg ? lo : hi;
+    const float q0 = rintf(__fdiv_rn(edge, s));
+    if (q0 != 0.0f) s = __fdiv_rn(edge, q0);
+    const float b = q0 == 0.0f ? 0.0f : edge;
+    const float qa = fminf(fmaxf(rintf(__fdiv_rn(__fsub_rn(v0, b), s)), 0.0f), 15.0f);
+    const float qb = fminf(fmaxf(rintf(__fdiv_rn(__fsub_rn(v1, b), s)), 0.0f), 15.0f);
+    q[(n * groups + g) * 32 + lane] = static_cast<uint8_t>(static_cast<uint32_t>(qa) | (static_cast<uint32_t>(qb) << 4));
+    if (lane == 0) {
+      scale[n * groups + g] = __float2bfloat16_rn(s);
+      bias[n * groups + g] = __float2bfloat16_rn(b);
+    }
+  }
+}
+
+// Split-half bytes [N, K/64, 32] -> sequential words [N, K/8] (element k = 8i + j at bits 4j..4j+3).
+__global__ void repack_int4_kernel(const uint8_t* in, uint32_t* out, int64_t words) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < words;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t group = i >> 3;
+    const int wi = static_cast<int>(i & 7);          // word of the group: elements 8 wi .. 8 wi + 7
+    const uint8_t* bytes = in + group * 32;
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = 8 * wi + j;                       // element of the group
+      const uint32_t nib = e < 32 ? (bytes[e] & 15u) : (bytes[e - 32] >> 4);
+      word |= nib << (4 * j);
+    }
+    out[i] = word;
+  }
+}
+
 // One warp per (row, group): symmetric int8.
 template <typename T>
 __global__ void quantize_int8_kernel(const T* w, int8_t* q, __nv_bfloat16* scale, int64_t N, int64_t K, int group) {
@@ -165,6 +223,43 @@ b200_status b200_quantize(b200_context* ctx, b200_stream stream, int bits, int g
           static_cast<const __nv_bfloat16*>(w), static_cast<int8_t*>(q_out), sc, N, K, group);
   }
   return EndLaunch(ctx, "b200_quantize");
+}
+
+b200_status b200_quantize_int4_ref(b200_context* ctx, b200_stream stream, const void* w, int w_dtype, void* q_out,
+                                   void* scale_out, void* bias_out, int64_t N, int64_t K) {
+  b200_status s = BeginLaunch(ctx);
+  if (s != B200_OK) return s;
+  if (w_dtype != B200_F32 && w_dtype != B200_BF16) return Fail(B200_UNIMPLEMENTED, "b200_quantize_int4_ref: w must be f32 or bf16");
+  if (N < 0 || K < 0) return Fail(B200_INVALID_ARGUMENT, "b200_quantize_int4_ref: negative size");
+  if (N == 0 || K == 0) return B200_OK;
+  if (K % 64 != 0) return Fail(B200_UNIMPLEMENTED, "b200_quantize_int4_ref: K=%lld is not a multiple of the group (64)", static_cast<long long>(K));
+  if (w == nullptr || q_out == nullptr || scale_out == nullptr || bias_out == nullptr)
+    return Fail(B200_INVALID_ARGUMENT, "b200_quantize_int4_ref: null buffer");
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<int64_t>(CeilDiv(N * (K / 64), threads / 32), 148 * 32));
+  if (w_dtype == B200_F32)
+    quantize_int4_ref_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(w), static_cast<uint8_t*>(q_out),
+                                                                    static_cast<__nv_bfloat16*>(scale_out),
+                                                                    static_cast<__nv_bfloat16*>(bias_out), N, K);
+  else
+    quantize_int4_ref_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q_out), static_cast<__nv_bfloat16*>(scale_out),
+        static_cast<__nv_bfloat16*>(bias_out), N, K);
+  return EndLaunch(ctx, "b200_quantize_int4_ref");
+}
+
+b200_status b200_repack_int4(b200_context* ctx, b200_stream stream, const void* q_split_half, void* q_sequential, int64_t N,
+                             int64_t K) {
+  b200_status s = BeginLaunch(ctx);
+  if (s != B200_OK) return s;
+  if (N < 0 || K < 0) return Fail(B200_INVALID_ARGUMENT, "b200_repack_int4: negative size");
+  if (N == 0 || K == 0) return B200_OK;
+  if (K % 64 != 0) return Fail(B200_UNIMPLEMENTED, "b200_repack_int4: K=%lld is not a multiple of 64", static_cast<long long>(K));
+  if (q_split_half == nullptr || q_sequential == nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_repack_int4: null buffer");
+  const int64_t words = N * (K / 8);
+  const int blocks = static_cast<int>(std::min<int64_t>(CeilDiv(words, 256), 148 * 16));
+  repack_int4_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(q_split_half), static_cast<uint32_t*>(q_sequential), words);
+  return EndLaunch(ctx, "b200_repack_int4");
 }
 
 }  // extern "C"

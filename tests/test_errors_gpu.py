@@ -54,3 +54,30 @@ def test_bad_device_ordinal():
     with pytest.raises(p.B200Error) as e:
         p.Context(1000)
     assert e.value.status == p._lib.INVALID_ARGUMENT
+
+
+def test_a_bounded_wait_that_runs_out_turns_into_a_sticky_timeout():
+    """A device-side wait with a short limit on a barrier nobody arrives at: the kernel gives up
+    and returns, the status word carries B200_TIMEOUT and the wait's id, the context's error is
+    sticky, and a fresh context on the same device works.  Nothing faults or hangs."""
+    import torch
+    p = pkg()
+    L, lib = p._lib, p.lib()
+    ctx = p.Context(0)
+    p._lib.check(lib.b200_context_wait_probe(ctx.handle, L.current_stream(), 200000))   # ~0.1 ms
+    torch.cuda.synchronize()
+    assert ctx.error() == L.TIMEOUT
+    msg = lib.b200_last_error()
+    assert b"TIMEOUT" in msg and b"900" in msg
+    x = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
+    st = lib.b200_rownorm(ctx.handle, L.current_stream(), 1, x.data_ptr(), None, None, x.data_ptr(), 4, 64, L.BF16, 1e-6)
+    assert st == L.TIMEOUT                                   # sticky: every later call on this context returns it
+    assert ctx.error() == L.TIMEOUT
+    fresh = p.Context(0)
+    p._lib.check(lib.b200_rownorm(fresh.handle, L.current_stream(), 1, x.data_ptr(), None, None, x.data_ptr(), 4, 64,
+                                  L.BF16, 1e-6))
+    torch.cuda.synchronize()
+    assert fresh.error() == 0
+    assert lib.b200_context_wait_probe(fresh.handle, L.current_stream(), 0) == L.INVALID_ARGUMENT
+    fresh.close()
+    ctx.close()

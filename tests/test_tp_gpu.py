@@ -90,3 +90,72 @@ def test_tp2_decoder_matches_oracle(peers, hidden, B):
     assert status == 0
     print(f"tp2 {peers} hidden {hidden} batch {B}: max logit error {err:.3e} x RMS")
     assert err <= 6e-2 and same_argmax and replay_equal
+
+
+def _timeout_worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from metal_pjrt_plugin_b200 import parallel
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = pkg.Context(rank)
+    tp = parallel.TensorParallel.from_torch_distributed(ctx)
+    B, E = 2, 256
+    tp.connect_peers(B * E)
+    dev = f"cuda:{rank}"
+    x = torch.ones((B, E), dtype=torch.bfloat16, device=dev)
+    gain = torch.ones((E,), dtype=torch.bfloat16, device=dev)
+    h = torch.empty_like(x)
+    tp.peer_partial(0, (B, E)).fill_(0.5)
+    tp.peer_partial(1, (B, E)).fill_(0.25)
+    torch.cuda.synchronize()
+    dist.barrier()
+    tp.sum_residual_norm(0, x, gain, h)            # exchange 1: both ranks take part
+    torch.cuda.synchronize()
+    ok_first = bool(torch.all(x == 2.0).item()) and ctx.error() == 0     # 1 + 0.5 + 0.5
+    dist.barrier()
+    status, message = 0, ""
+    if rank == 0:
+        # exchange 2: the peer stays alive (it waits at the host barrier below) but never joins
+        tp.sum_residual_norm(1, x, gain, h)
+        torch.cuda.synchronize()                    # the wait runs out after about two seconds; the kernel returns
+        status = ctx.error()
+        message = pkg.lib().b200_last_error().decode()
+        untouched = bool(torch.all(x == 2.0).item())     # nothing was summed, nothing written
+    else:
+        untouched = True
+    dist.barrier()                                  # both ranks leave together, with nothing in flight
+    out_q.put((rank, (ok_first, status, message, untouched)))
+    tp.close()
+    dist.destroy_process_group()
+
+
+def test_tp2_exchange_wait_runs_out_when_a_peer_skips_an_exchange():
+    """Rank 1 stays alive but skips one exchange: rank 0's bounded wait for its flag expires,
+    the kernel reads nothing of the peer, writes nothing, reports B200_TIMEOUT with the peer's
+    wait id, and both ranks then tear down normally.  No GPU faults or hangs."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from util import pkg
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000 + 101
+    procs = [ctx.Process(target=_timeout_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p_ in procs:
+        p_.start()
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p_ in procs:
+        p_.join(timeout=120)
+        assert p_.exitcode == 0
+    TIMEOUT = pkg()._lib.TIMEOUT
+    ok_first, status, message, untouched = res[0]
+    assert ok_first and res[1][0]
+    assert status == TIMEOUT and "401" in message and untouched
+    assert res[1][1] == 0
