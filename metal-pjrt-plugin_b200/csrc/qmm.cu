@@ -216,7 +216,7 @@ __device__ __forceinline__ void consumer_barrier() {
 }
 
 // One output element: the per-channel scale (if any), then the epilogue.
-template <int FMT, bool GROUPED>
+template <int FMT, bool GROUPED, bool TP = false>
 __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, int n) {
   if (!GROUPED && Fmt<FMT>::kBits != 16) v *= ldg_bf16(a.scale + n);
   if (FMT == kBf16 && a.epilogue == kEpilogueGemm) {   // b200_gemm's few-row route: 16-bit weights only
@@ -236,7 +236,7 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
   }
   const float y = bf16_round(v);
   const size_t o = static_cast<size_t>(m) * a.ldo + n;
-  if (a.epilogue == kEpiloguePush) {
+  if (TP && a.epilogue == kEpiloguePush) {
     // plain stores into every rank's memory (its own included); the slot alternates with the exchange number
     const size_t so_ = static_cast<size_t>((*a.tp_count + 1u) & 1u) * a.tp_world * a.tp_cap + o;
 #pragma unroll
@@ -270,7 +270,9 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
 // LEAN: launched only without a K split and with 16-byte-loadable x, gain, scales and offsets, so
 // none of the code for the other cases is compiled in (the unrolled variants, KG > 0, are always lean).
 // VEC: the 16-byte-load assumption alone, for the builds that do split K (LEAN implies it).
-template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN>
+// TP: the build that takes part in the tensor-parallel exchange (sums the ranks' partial sums while it
+// stages x, or pushes its own from the epilogue); the others carry none of that code.
+template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN, bool TP = false>
 __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
   static_assert(KG == 0 || LEAN, "the unrolled variants are lean");
   static_assert(!LEAN || VEC, "lean implies 16-byte loads");
@@ -429,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     // peers' flags say when their partials have landed here.  After a wait that gave up nothing of
     // a peer is touched (the sums only ever read this rank's own memory) and the status word says so.
     const float* tp_slot = nullptr;
-    if (a.tp_src != nullptr) {
+    if (TP && a.tp_src != nullptr) {
       const uint32_t n = *a.tp_count;
       tp_slot = a.tp_src + static_cast<size_t>(n & 1u) * a.tp_world * a.tp_cap;
       if (tid < a.tp_world && tid != a.tp_rank) {
@@ -453,7 +455,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         dst[2 * j] = bf16_lo(w[j]);
         dst[2 * j + 1] = bf16_hi(w[j]);
       }
-      if (tp_slot != nullptr) {
+      if (TP && tp_slot != nullptr) {
         float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
         const float* base = tp_slot + static_cast<size_t>(m) * a.K + k;
 #pragma unroll
@@ -483,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         ss[m] = 0.0f;
         if (m < a.M) {
           const __nv_bfloat16* xr = a.x + static_cast<size_t>(m) * a.ldx;
-          if (x_vec && tp_slot != nullptr) {
+          if (TP && x_vec && tp_slot != nullptr) {
             for (int i = tid * 8; i < a.K; i += kConsumerThreads * 8) {
               float e8[8];
               load_x8(m, i, e8);
@@ -550,7 +552,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             }
           };
         const __nv_bfloat16* xr = a.x + static_cast<size_t>(valid ? um : 0) * a.ldx;
-        if (valid && tp_slot != nullptr) {
+        if (TP && valid && tp_slot != nullptr) {
           load_x8(um, kbase + run0, e);
           load_x8(um, kbase + run1, e + 8);
           if (blockIdx.x == 0 && a.x_out != nullptr) {   // the new residual row, once (each K slice by its CTA of tile 0)
@@ -800,10 +802,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             v.z += part[c].z;
             v.w += part[c].w;
           }
-          store_output<FMT, GROUPED>(a, v.x, m, n0 + r);
-          store_output<FMT, GROUPED>(a, v.y, m + 1, n0 + r);
-          store_output<FMT, GROUPED>(a, v.z, m + 2, n0 + r);
-          store_output<FMT, GROUPED>(a, v.w, m + 3, n0 + r);
+          store_output<FMT, GROUPED, TP>(a, v.x, m, n0 + r);
+          store_output<FMT, GROUPED, TP>(a, v.y, m + 1, n0 + r);
+          store_output<FMT, GROUPED, TP>(a, v.z, m + 2, n0 + r);
+          store_output<FMT, GROUPED, TP>(a, v.w, m + 3, n0 + r);
         }
         return;
       }
@@ -816,7 +818,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         float v = 0.0f;
 #pragma unroll
         for (int c = 0; c < 8; ++c) v += part[c];
-        store_output<FMT, GROUPED>(a, v, m, n0 + r);
+        store_output<FMT, GROUPED, TP>(a, v, m, n0 + r);
       }
     };
 
@@ -936,14 +938,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
             float v = 0.0f;
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) v += red_cur[(w * R + r) * MP + m];
-            store_output<FMT, GROUPED>(a, v, m, n0 + r);
+            store_output<FMT, GROUPED, TP>(a, v, m, n0 + r);
           }
         } else {
           for (int idx = tid; idx < rows_valid * a.M; idx += kConsumerThreads) {
             const int r = idx % rows_valid, m = idx / rows_valid;
             const float v = red_cur[r * RP + m];
             red_cur[r * RP + m] = 0.0f;   // this buffer is added into again two tiles from now
-            store_output<FMT, GROUPED>(a, v, m, n0 + r);
+            store_output<FMT, GROUPED, TP>(a, v, m, n0 + r);
           }
         }
       } else {
@@ -965,7 +967,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       cluster_arrive(n_my);
       cluster_wait(n_my);
     }
-    if (a.epilogue == kEpiloguePush) {
+    if (TP && a.epilogue == kEpiloguePush) {
       // The last CTA of this rank to finish closes the exchange: it counts it and raises this
       // rank's flag on every peer.  (Every CTA read the old count before it got here.)
       consumer_barrier();
@@ -1111,9 +1113,9 @@ b200_status MakePlan(const b200_qmm_params* p, int sm_count, int max_smem, Plan*
   return MakePlanImpl(p, sm_count, max_smem, out, false);
 }
 
-template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN>
+template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN, bool TP = false>
 cudaError_t LaunchOne(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
-  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG, LEAN, VEC>;
+  auto kernel = qgemv_kernel<FMT, MB, RT, GROUPED, KG, LEAN, VEC, TP>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
   if (e != cudaSuccess) return e;
   LaunchCfg lc;
@@ -1161,6 +1163,20 @@ bool FastPathOk(const QmmArgs& a) {
 template <int FMT, bool GROUPED>
 cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
   const bool vec = args.x_vec && (!GROUPED || args.scale_vec);   // 16-byte loads of x, scales and offsets
+  if (args.tp_world > 0) {
+    // The exchange builds: sequential int4 in groups, up to 8 rows, 16-byte loads (what a sharded decoder has).
+    if constexpr (FMT == kInt4Seq && GROUPED) {
+      if (pl.mb != 1 || !vec) return cudaErrorInvalidValue;
+      const bool fast = args.k_per_cta == 64 * kGroupK && pl.split == 1 && FastPathOk<GROUPED>(args);
+      if (pl.rt == 2) return fast ? LaunchOne<FMT, 1, 2, GROUPED, 64, true, true, true>(pl, args, grid, stream) : cudaErrorInvalidValue;
+      if (pl.rt != 1) return cudaErrorInvalidValue;
+      if (fast) return LaunchOne<FMT, 1, 1, GROUPED, 64, true, true, true>(pl, args, grid, stream);
+      if (pl.split == 1) return LaunchOne<FMT, 1, 1, GROUPED, 0, true, true, true>(pl, args, grid, stream);
+      return LaunchOne<FMT, 1, 1, GROUPED, 0, false, true, true>(pl, args, grid, stream);
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
   switch (pl.mb * 10 + pl.rt) {
     case 11:
       // the decode shape K = 4096 (64 groups, no K split) takes the unrolled register path
@@ -1319,6 +1335,8 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   if (tp != nullptr && tp->world > 1) {
     if (tp->push && tp->src != nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: a projection either pushes partial sums or consumes them");
     if (p->M * p->N > tp->cap && tp->push) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: partial sums exceed the exchange block");
+    if (pl.fmt != kInt4Seq || pl.mb != 1 || !a.x_vec || !a.scale_vec)
+      return Fail(B200_UNIMPLEMENTED, "b200_qmm: the exchange takes sequential int4 weights, up to 8 rows, 16-byte aligned operands");
     a.tp_world = tp->world;
     a.tp_rank = tp->rank;
     a.tp_cap = tp->cap;
