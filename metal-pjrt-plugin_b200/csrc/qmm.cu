@@ -96,12 +96,10 @@ struct QmmArgs {
   const __nv_bfloat16* gain;   // RMSNorm gain [K]
   // tensor-parallel exchange (tp_world == 0: none), see b200::QmmTp
   int tp_world, tp_rank;
-  float* tp_dst[kTpMaxWorld];            // epilogue kEpiloguePush: slot 0 of this rank's sub-slot on every rank
-  uint32_t* tp_peer_flags[kTpMaxWorld];  // ... and the flag arrays to raise there
+  uint2* tp_dst[kTpMaxWorld];            // epilogue kEpiloguePush: slot 0 of this rank's sub-slot on every rank
   uint32_t* tp_count;                    // exchanges this rank has pushed (device memory)
   uint32_t* tp_done;                     // CTAs of the pushing kernel that have finished
-  const float* tp_src;                   // prologue: slot 0 of the partials in this rank's memory, [world][cap]
-  const uint32_t* tp_flags;              // ... and the flags the peers raise here
+  const uint2* tp_src;                   // prologue: slot 0 of the lines in this rank's memory, [world][cap]
   long long tp_cap;                      // floats per sub-slot; a slot is world sub-slots
   __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
 };
@@ -109,13 +107,45 @@ struct QmmArgs {
 constexpr int kEpilogueGemm = 100;
 constexpr int kEpiloguePush = 101;   // f32 partial sums stored into every rank's exchange block
 
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// The exchange moves 8-byte lines {f32 partial sum, exchange number}: one store carries the value
+// and says which exchange it belongs to, so the reader needs no flag of its own, no fence and no
+// "last CTA" on the writer's side; it just reads the line again until the number is the one it wants.
+__device__ __forceinline__ void st_line(uint2* p, float v, uint32_t n) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint4 ld_lines2(const uint2* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Eight consecutive lines of exchange n (p 16-byte aligned).  Waits, bounded, for lines that have not
+// landed yet; once any wait of this context has run out (the status word is set) nobody waits again.
+// false: the values are not the peers' (zeros are returned).
+__device__ __forceinline__ bool ld_lines8(const uint2* p, uint32_t n, int* status, int where, float* out) {
+  uint4 v[4];
+  long long t0 = 0;
+  bool ok;
+  for (;;) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = ld_lines2(p + 2 * j);
+    ok = true;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ok = ok && v[j].y == n && v[j].w == n;
+    if (ok) break;
+    if (*reinterpret_cast<volatile int*>(status) != 0) break;
+    if (t0 == 0) {
+      t0 = clock64();
+    } else if (clock64() - t0 > 4000000000ll) {
+      report_timeout(status, where);
+      break;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    out[2 * j] = ok ? __uint_as_float(v[j].x) : 0.0f;
+    out[2 * j + 1] = ok ? __uint_as_float(v[j].z) : 0.0f;
+  }
+  return ok;
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -237,11 +267,12 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
   const float y = bf16_round(v);
   const size_t o = static_cast<size_t>(m) * a.ldo + n;
   if (TP && a.epilogue == kEpiloguePush) {
-    // plain stores into every rank's memory (its own included); the slot alternates with the exchange number
-    const size_t so_ = static_cast<size_t>((*a.tp_count + 1u) & 1u) * a.tp_world * a.tp_cap + o;
+    // one line per value into every rank's memory (its own included); the slot alternates with the exchange number
+    const uint32_t n_x = *a.tp_count + 1u;
+    const size_t so_ = static_cast<size_t>(n_x & 1u) * a.tp_world * a.tp_cap + o;
 #pragma unroll
     for (int r = 0; r < kTpMaxWorld; ++r)
-      if (r < a.tp_world) a.tp_dst[r][so_] = v;
+      if (r < a.tp_world) st_line(a.tp_dst[r] + so_, v, n_x);
     return;
   }
   if (a.epilogue == B200_QMM_OUT_F32_RAW) {
@@ -426,25 +457,15 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     scale_store(static_cast<int>(blockIdx.x) * R, so);
     pdl_wait();  // x (and the residual) come from the previous kernel
     // Tensor parallel: x is the old residual; the new one is x + bf16(sum over ranks of the partial
-    // sums that the K-sharded projection before this one pushed into every rank's memory).  That
-    // kernel has finished on this rank (the wait above), so the exchange number is final; the
-    // peers' flags say when their partials have landed here.  After a wait that gave up nothing of
-    // a peer is touched (the sums only ever read this rank's own memory) and the status word says so.
-    const float* tp_slot = nullptr;
+    // sums that the K-sharded projection before this one pushed into every rank's memory as
+    // {value, exchange number} lines).  That kernel has finished on this rank (the wait above), so
+    // the exchange number is final; a peer's line that has not landed yet is read again (bounded).
+    // Only this rank's own memory is ever read.
+    const uint2* tp_slot = nullptr;
+    uint32_t tp_n = 0;
     if (TP && a.tp_src != nullptr) {
-      const uint32_t n = *a.tp_count;
-      tp_slot = a.tp_src + static_cast<size_t>(n & 1u) * a.tp_world * a.tp_cap;
-      if (tid < a.tp_world && tid != a.tp_rank) {
-        bool ok = false;
-        const long long t0 = clock64();
-        for (;;) {
-#pragma unroll 1
-          for (int i = 0; i < 64 && !ok; ++i) ok = static_cast<int32_t>(ld_acquire_sys_u32(a.tp_flags + tid) - n) >= 0;
-          if (ok || clock64() - t0 > 4000000000ll) break;
-        }
-        if (!ok) report_timeout(a.status, 400 + tid);
-      }
-      consumer_barrier();
+      tp_n = *a.tp_count;
+      tp_slot = a.tp_src + static_cast<size_t>(tp_n & 1u) * a.tp_world * a.tp_cap;
     }
     // eight values of row m starting at k, the partial sums folded in
     auto load_x8 = [&](int m, int k, float* dst) {
@@ -457,15 +478,13 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       }
       if (TP && tp_slot != nullptr) {
         float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        const float* base = tp_slot + static_cast<size_t>(m) * a.K + k;
+        const uint2* base = tp_slot + static_cast<size_t>(m) * a.K + k;
+#pragma unroll 1
+        for (int r = 0; r < a.tp_world; ++r) {   // rank order on every rank: identical sums everywhere
+          float part[8];
+          ld_lines8(base + static_cast<size_t>(r) * a.tp_cap, tp_n, a.status, 400 + r, part);
 #pragma unroll
-        for (int r = 0; r < kTpMaxWorld; ++r) {   // rank order on every rank: identical sums everywhere
-          if (r < a.tp_world) {
-            const float4 p0 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(r) * a.tp_cap));
-            const float4 p1 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(r) * a.tp_cap) + 1);
-            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
-            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
-          }
+          for (int j = 0; j < 8; ++j) sum[j] += part[j];
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) dst[j] = bf16_round(dst[j] + bf16_round(sum[j]));
@@ -968,18 +987,15 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       cluster_wait(n_my);
     }
     if (TP && a.epilogue == kEpiloguePush) {
-      // The last CTA of this rank to finish closes the exchange: it counts it and raises this
-      // rank's flag on every peer.  (Every CTA read the old count before it got here.)
+      // The last CTA of this rank to finish counts the exchange (every CTA read the old count
+      // before it got here).  Nothing else closes it: each line says which exchange it is.
       consumer_barrier();
       if (tid == 0) {
         const uint32_t n = *a.tp_count + 1u;
-        __threadfence_system();   // this CTA's stores into the peers, before it is counted as finished
+        __threadfence();
         if (atomicAdd(a.tp_done, 1u) == gridDim.x * gridDim.y - 1u) {
           *a.tp_done = 0u;
           *a.tp_count = n;
-          __threadfence_system();
-          for (int r = 0; r < a.tp_world; ++r)
-            if (r != a.tp_rank) st_release_sys_u32(a.tp_peer_flags[r] + a.tp_rank, n);
         }
       }
     }
@@ -1164,15 +1180,17 @@ template <int FMT, bool GROUPED>
 cudaError_t LaunchFmt(const Plan& pl, const QmmArgs& args, dim3 grid, cudaStream_t stream) {
   const bool vec = args.x_vec && (!GROUPED || args.scale_vec);   // 16-byte loads of x, scales and offsets
   if (args.tp_world > 0) {
-    // The exchange builds: sequential int4 in groups, up to 8 rows, 16-byte loads (what a sharded decoder has).
-    if constexpr (FMT == kInt4Seq && GROUPED) {
-      if (pl.mb != 1 || !vec) return cudaErrorInvalidValue;
+    // The exchange builds: sequential int4 in groups (the projections) and bf16 (the LM head), up to
+    // 8 rows: what a sharded decoder has.
+    if constexpr ((FMT == kInt4Seq && GROUPED) || FMT == kBf16) {
+      if (pl.mb != 1) return cudaErrorInvalidValue;
       const bool fast = args.k_per_cta == 64 * kGroupK && pl.split == 1 && FastPathOk<GROUPED>(args);
       if (pl.rt == 2) return fast ? LaunchOne<FMT, 1, 2, GROUPED, 64, true, true, true>(pl, args, grid, stream) : cudaErrorInvalidValue;
       if (pl.rt != 1) return cudaErrorInvalidValue;
       if (fast) return LaunchOne<FMT, 1, 1, GROUPED, 64, true, true, true>(pl, args, grid, stream);
-      if (pl.split == 1) return LaunchOne<FMT, 1, 1, GROUPED, 0, true, true, true>(pl, args, grid, stream);
-      return LaunchOne<FMT, 1, 1, GROUPED, 0, false, true, true>(pl, args, grid, stream);
+      if (pl.split == 1 && vec) return LaunchOne<FMT, 1, 1, GROUPED, 0, true, true, true>(pl, args, grid, stream);
+      if (vec) return LaunchOne<FMT, 1, 1, GROUPED, 0, false, true, true>(pl, args, grid, stream);
+      return LaunchOne<FMT, 1, 1, GROUPED, 0, false, false, true>(pl, args, grid, stream);
     } else {
       return cudaErrorInvalidValue;
     }
@@ -1325,18 +1343,16 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   a.tp_rank = 0;
   a.tp_count = a.tp_done = nullptr;
   a.tp_src = nullptr;
-  a.tp_flags = nullptr;
   a.tp_cap = 0;
   a.x_out = nullptr;
   for (int r = 0; r < kTpMaxWorld; ++r) {
     a.tp_dst[r] = nullptr;
-    a.tp_peer_flags[r] = nullptr;
   }
   if (tp != nullptr && tp->world > 1) {
     if (tp->push && tp->src != nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: a projection either pushes partial sums or consumes them");
     if (p->M * p->N > tp->cap && tp->push) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: partial sums exceed the exchange block");
-    if (pl.fmt != kInt4Seq || pl.mb != 1 || !a.x_vec || !a.scale_vec)
-      return Fail(B200_UNIMPLEMENTED, "b200_qmm: the exchange takes sequential int4 weights, up to 8 rows, 16-byte aligned operands");
+    if ((pl.fmt != kInt4Seq && pl.fmt != kBf16) || pl.mb != 1)
+      return Fail(B200_UNIMPLEMENTED, "b200_qmm: the exchange takes sequential int4 or bf16 weights and up to 8 rows");
     a.tp_world = tp->world;
     a.tp_rank = tp->rank;
     a.tp_cap = tp->cap;
@@ -1348,13 +1364,11 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
       a.tp_done = tp->done;
       for (int r = 0; r < tp->world; ++r) {
         a.tp_dst[r] = tp->dst[r];
-        a.tp_peer_flags[r] = tp->peer_flags[r];
       }
     } else if (tp->src != nullptr) {
       if (p->prologue != B200_QMM_PRO_RMSNORM || !a.x_vec || a.ldx != a.K || a.K % 8 != 0 || p->M * p->K > tp->cap)
         return Fail(B200_INVALID_ARGUMENT, "b200_qmm: summing the ranks' partial sums goes with the RMSNorm prologue on dense, aligned rows");
       a.tp_src = tp->src;
-      a.tp_flags = tp->flags;
       a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
     }
   }

@@ -184,11 +184,11 @@ __global__ void __launch_bounds__(1024) peer_sum_residual_norm_kernel(const Peer
 }
 
 size_t BlockBytes(int64_t cap, int world) {
-  return static_cast<size_t>(2 + 2 * world) * cap * sizeof(float) + 2 * (kTpMaxWorld + 2) * sizeof(uint32_t);
+  return static_cast<size_t>(2 + 4 * world) * cap * sizeof(float) + 2 * (kTpMaxWorld + 2) * sizeof(uint32_t);
 }
-float* PushedOf(void* block, int64_t cap) { return static_cast<float*>(block) + 2 * cap; }
+uint2* PushedOf(void* block, int64_t cap) { return reinterpret_cast<uint2*>(static_cast<float*>(block) + 2 * cap); }
 uint32_t* FlagsOf(void* block, int64_t cap, int world) {
-  return reinterpret_cast<uint32_t*>(static_cast<float*>(block) + static_cast<size_t>(2 + 2 * world) * cap);
+  return reinterpret_cast<uint32_t*>(static_cast<float*>(block) + static_cast<size_t>(2 + 4 * world) * cap);
 }
 uint32_t* PushFlagsOf(void* block, int64_t cap, int world) { return FlagsOf(block, cap, world) + kTpMaxWorld + 2; }
 
@@ -225,7 +225,7 @@ b200_status TpAllGather(b200_tp* tp, cudaStream_t stream, const void* send, void
 }
 
 bool TpPushLink(b200_tp* tp, QmmTp* out) {
-  if (tp == nullptr || !tp->peer || out == nullptr) return false;
+  if (tp == nullptr || !tp->peer || out == nullptr || tp->cap % 8 != 0) return false;   // (16-byte reads of the lines)
   *out = QmmTp();
   out->world = tp->world;
   out->rank = tp->rank;
@@ -234,10 +234,8 @@ bool TpPushLink(b200_tp* tp, QmmTp* out) {
   out->count = pf + kTpMaxWorld;
   out->done = pf + kTpMaxWorld + 1;
   out->src = PushedOf(tp->block, tp->cap);
-  out->flags = pf;
   for (int r = 0; r < tp->world; ++r) {
     out->dst[r] = PushedOf(tp->peer_block[r], tp->cap) + static_cast<int64_t>(tp->rank) * tp->cap;
-    out->peer_flags[r] = PushFlagsOf(tp->peer_block[r], tp->cap, tp->world);
   }
   return true;
 }

@@ -6,13 +6,14 @@ constexpr int kTpMaxWorld = 8;
 
 // One rank's peer-exchange block (device memory, mapped into every peer by CUDA IPC):
 //   float partial[2][cap]          two alternating slots of this rank's partial sums (pulled by the peers)
-//   float pushed[2][world][cap]    two alternating slots of EVERY rank's partial sums, stored here by
-//                                  the projections of those ranks (rank r writes sub-slot r)
+//   uint2 pushed[2][world][cap]    two alternating slots of EVERY rank's partial sums, stored here by
+//                                  the projections of those ranks (rank r writes sub-slot r) as 8-byte
+//                                  lines {f32 bits, number of the push exchange the value belongs to}
 //   uint32 flags[kTpMaxWorld]      flags[r]: last pull exchange for which rank r's partial is ready
 //                                  (written by rank r over NVLink)
 //   uint32 seq                     pull exchanges this rank has completed
 //   uint32 done                    CTAs of the running pull exchange that have finished
-//   uint32 pflags[kTpMaxWorld]     pflags[r]: last push exchange whose partial sums from rank r have landed here
+//   uint32 unused[kTpMaxWorld]
 //   uint32 pcount                  push exchanges this rank has pushed
 //   uint32 pdone                   CTAs of the pushing projection that have finished
 struct b200_tp {
@@ -27,22 +28,21 @@ struct b200_tp {
 
 namespace b200 {
 // How one projection (b200_qmm) takes part in the push exchange of a K-sharded product's
-// partial sums.  push: its epilogue stores the raw f32 partial sums into sub-slot `rank` of
-// every rank's block (plain stores over NVLink) and the last CTA raises this rank's flag on
-// every peer.  src: its RMSNorm prologue first waits (bounded) for every peer's flag, then reads
-// x as bf16(x + bf16(sum over ranks, in rank order, of the sub-slots in THIS rank's memory));
-// the CTAs of its first row tile write those new residual rows to x_out.  Slots alternate with
-// the exchange number, which lives in device memory (a captured graph replays).
+// partial sums.  push: its epilogue stores each raw f32 partial sum, together with the number
+// of the exchange, as one 8-byte line into sub-slot `rank` of every rank's block (plain
+// stores over NVLink; no flag, no fence: the line itself says when it is there).  src: its
+// RMSNorm prologue reads x as bf16(x + bf16(sum over ranks, in rank order, of the sub-slots in
+// THIS rank's memory)), reading a line again (bounded) until it carries the expected exchange
+// number; the CTAs of its first row tile write those new residual rows to x_out.  Slots
+// alternate with the exchange number, which lives in device memory (a captured graph replays).
 struct QmmTp {
   int world = 0, rank = 0;
-  int64_t cap = 0;                        // floats per sub-slot
+  int64_t cap = 0;                        // lines per sub-slot
   uint32_t* count = nullptr;              // push exchanges so far
   bool push = false;
-  float* dst[kTpMaxWorld] = {};           // this rank's sub-slot (of slot 0) on every rank
-  uint32_t* peer_flags[kTpMaxWorld] = {}; // pflags of every rank
+  uint2* dst[kTpMaxWorld] = {};           // this rank's sub-slot (of slot 0) on every rank
   uint32_t* done = nullptr;
-  const float* src = nullptr;             // slot 0 of pushed[][][] in this rank's memory
-  const uint32_t* flags = nullptr;        // this rank's pflags
+  const uint2* src = nullptr;             // slot 0 of pushed[][][] in this rank's memory
   void* x_out = nullptr;
 };
 b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_params* p, const QmmTp* tp);

@@ -1,8 +1,10 @@
 """Tensor-parallel decoder on 2 GPUs (one process per GPU, NCCL through the library)
 against the unsharded CPU oracle.  Skipped where fewer than two devices are visible.
 Ranks leave only after the step has been synchronised; NVLS is switched off for NCCL."""
+import datetime
 import os
 import sys
+import traceback
 
 import numpy as np
 import pytest
@@ -12,7 +14,40 @@ from util import ROOT
 pytestmark = pytest.mark.gpu
 
 
+def _guarded(body, rank, out_q, *args):
+    """A rank that raises says so through the queue at once, so the test fails in seconds
+    instead of waiting for its own limit."""
+    try:
+        body(rank, *args)
+    except BaseException:
+        out_q.put((rank, ("error", traceback.format_exc())))
+        raise
+
+
 def _worker(rank, world, port, out_q, peers, hidden, B):
+    _guarded(_worker_body, rank, out_q, world, port, out_q, peers, hidden, B)
+
+
+def _timeout_worker(rank, world, port, out_q):
+    _guarded(_timeout_worker_body, rank, out_q, world, port, out_q)
+
+
+def _collect(q, procs):
+    res = {}
+    for _ in procs:
+        rank, r = q.get(timeout=200)
+        if isinstance(r, tuple) and len(r) == 2 and r[0] == "error":
+            for p_ in procs:
+                p_.join(timeout=100)
+            pytest.fail(f"rank {rank} raised:\n{r[1]}")
+        res[rank] = r
+    for p_ in procs:
+        p_.join(timeout=120)
+        assert p_.exitcode == 0
+    return res
+
+
+def _worker_body(rank, world, port, out_q, peers, hidden, B):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     if peers == "pull":   # the separate exchange kernel instead of the push from the projections' epilogue
         os.environ["B200_TP_PULL"] = "1"
@@ -30,7 +65,7 @@ def _worker(rank, world, port, out_q, peers, hidden, B):
     pkg = load_package()
     from metal_pjrt_plugin_b200 import parallel
     torch.cuda.set_device(rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=90))
     ctx = pkg.Context(rank)
     tp = parallel.TensorParallel.from_torch_distributed(ctx)
     if peers:   # the sums over ranks over peer memory instead of NCCL
@@ -82,17 +117,14 @@ def test_tp2_decoder_matches_oracle(peers, hidden, B):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peers, hidden, B)) for r in range(2)]
     for p_ in procs:
         p_.start()
-    res = dict(q.get(timeout=300) for _ in range(2))
-    for p_ in procs:
-        p_.join(timeout=120)
-        assert p_.exitcode == 0
+    res = _collect(q, procs)
     err, same_argmax, replay_equal, status = res[0]
     assert status == 0
     print(f"tp2 {peers} hidden {hidden} batch {B}: max logit error {err:.3e} x RMS")
     assert err <= 6e-2 and same_argmax and replay_equal
 
 
-def _timeout_worker(rank, world, port, out_q):
+def _timeout_worker_body(rank, world, port, out_q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -102,7 +134,7 @@ def _timeout_worker(rank, world, port, out_q):
     pkg = load_package()
     from metal_pjrt_plugin_b200 import parallel
     torch.cuda.set_device(rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=90))
     ctx = pkg.Context(rank)
     tp = parallel.TensorParallel.from_torch_distributed(ctx)
     B, E = 2, 256
@@ -150,10 +182,7 @@ def test_tp2_exchange_wait_runs_out_when_a_peer_skips_an_exchange():
     procs = [ctx.Process(target=_timeout_worker, args=(r, 2, port, q)) for r in range(2)]
     for p_ in procs:
         p_.start()
-    res = dict(q.get(timeout=300) for _ in range(2))
-    for p_ in procs:
-        p_.join(timeout=120)
-        assert p_.exitcode == 0
+    res = _collect(q, procs)
     TIMEOUT = pkg()._lib.TIMEOUT
     ok_first, status, message, untouched = res[0]
     assert ok_first and res[1][0]
