@@ -174,8 +174,13 @@ b200_status b200_matmul_execute(b200_context* ctx, b200_stream stream, const b20
  *            nibble_order 1: q uint8 [N, K/64, 32], low nibble = element j of the
  *            group, high nibble = element j+32 (qwen3.py:169-196);
  *            scale, bias bf16 [N, K/64].
- * M <= 32 runs the streaming kernel; larger M is refused (dequantise, then GEMM,
- * like the reference beyond ROWS_MAX, qwen3.py:210-230). */
+ * M <= 32 runs the streaming kernel.  Larger M (prefill-sized batches) dequantises the
+ * weights, panel by panel, into a bf16 workspace of the context that stays in L2 and runs the
+ * tcgen05 GEMM on each panel (like the reference beyond ROWS_MAX: dequantize, then x @ w.T,
+ * qwen3.py:199-230); there the weights are rounded to bf16 before the product, no prologue
+ * is fused, the epilogue is OUT_BF16, ADD_RESIDUAL (one rounding of acc + residual) or
+ * OUT_F32_RAW, and the workspace (at most 32 MB) is allocated on the first such call of a
+ * context: make that call outside a stream capture. */
 typedef enum { B200_QMM_OUT_BF16 = 0,      /* out bf16 [M, ldo] */
                B200_QMM_ADD_RESIDUAL = 1,  /* out = bf16(residual + bf16(y)), residual bf16 [M, ldo] */
                B200_QMM_OUT_F32 = 2,       /* out f32 [M, ldo] holding the bf16-rounded value */
@@ -208,6 +213,11 @@ typedef struct {
   const void* prologue_gain; /* RMSNORM: bf16 [K] */
 } b200_qmm_params;
 
+/* Which kernel b200_qmm_run takes for sequential int4 in groups of 64 with up to 8 rows of x:
+ * 0 the library's choice (the mma.sync streaming kernel, unless B200_QMM_TC=1 is set), 1 the
+ * mma.sync kernel, 2 the tcgen05 kernel (nibbles spread to e4m3 bytes in tensor memory,
+ * activations split into two e4m3 terms) wherever it applies.  For tests and measurements. */
+void b200_qmm_force_route(b200_context* ctx, int route);
 b200_status b200_qmm_validate(const b200_qmm_params* p);
 b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_params* p);
 /* The short form: dense rows, bf16 in and out. */

@@ -31,6 +31,15 @@ struct b200_context {
   std::atomic<int64_t> launches{0};
   std::atomic<int64_t> fail_at{0};  // absolute launch index to refuse, 0 = disarmed
   std::atomic<int> force_route{0};
+  std::atomic<int> qmm_route{0};   // b200_qmm_force_route
+  void* qmm_ws = nullptr;          // bf16 panel of dequantised weights (b200_qmm above 32 rows), grown on first use
+  size_t qmm_ws_bytes = 0;
+  // scratch of the tensor-core dequant-matmul: partial rows of tiles shared between CTAs, and per
+  // tile how many CTAs have delivered theirs (zero between launches)
+  float* qtc_parts = nullptr;
+  size_t qtc_parts_floats = 0;
+  unsigned* qtc_counters = nullptr;
+  int qtc_tiles_max = 0;
   std::mutex mu;
   std::string sticky_message;
 };

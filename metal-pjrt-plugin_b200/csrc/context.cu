@@ -135,9 +135,16 @@ b200_status b200_context_create(int device_ordinal, b200_context** out) {
   e = cudaMalloc(&ctx->dev_status, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMallocHost(&ctx->host_status, 4 * sizeof(int));
+  ctx->qtc_parts_floats = 4u << 20;   // 16 MB
+  ctx->qtc_tiles_max = 1 << 16;
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->qtc_parts, ctx->qtc_parts_floats * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->qtc_counters, ctx->qtc_tiles_max * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(ctx->qtc_counters, 0, ctx->qtc_tiles_max * sizeof(unsigned));
   if (e != cudaSuccess) {
     b200_status s = Fail(B200_RESOURCE_EXHAUSTED, "context allocation: %s", cudaGetErrorString(e));
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->qtc_parts) cudaFree(ctx->qtc_parts);
+    if (ctx->qtc_counters) cudaFree(ctx->qtc_counters);
     delete ctx;
     return s;
   }
@@ -150,6 +157,9 @@ void b200_context_destroy(b200_context* ctx) {
   if (ctx == nullptr) return;
   cudaSetDevice(ctx->device);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->qtc_parts) cudaFree(ctx->qtc_parts);
+  if (ctx->qtc_counters) cudaFree(ctx->qtc_counters);
+  if (ctx->qmm_ws) cudaFree(ctx->qmm_ws);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
   delete ctx;
 }
@@ -189,6 +199,10 @@ void b200_context_fail_launch_after(b200_context* ctx, int64_t n) {
 }
 
 int64_t b200_context_launch_count(b200_context* ctx) { return ctx == nullptr ? 0 : ctx->launches.load(); }
+
+void b200_qmm_force_route(b200_context* ctx, int route) {
+  if (ctx != nullptr) ctx->qmm_route.store(route);
+}
 
 void b200_gemm_force_route(b200_context* ctx, int route) {
   if (ctx != nullptr) ctx->force_route.store(route);

@@ -29,6 +29,8 @@
 #include <map>
 #include <utility>
 
+#include "qmm_many.cuh"
+#include "qmm_tc.cuh"
 #include "tp.cuh"
 
 namespace cg = cooperative_groups;
@@ -1033,10 +1035,11 @@ b200_status Validate(const b200_qmm_params* p) {
   if (p->bits != 4 && p->bits != 8 && p->bits != 16)
     return Fail(B200_INVALID_ARGUMENT, "b200_qmm: bits must be 4, 8 or 16, got %d", p->bits);
   if (p->M < 0 || p->N < 0 || p->K < 0) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: negative size");
-  if (p->M > 32)
-    return Fail(B200_UNIMPLEMENTED,
-                "b200_qmm: M = %lld rows; the streaming kernel takes up to 32 (dequantise, then b200_gemm)",
+  if (p->M > 32 && p->prologue != B200_QMM_PRO_NONE)
+    return Fail(B200_UNIMPLEMENTED, "b200_qmm: the fused input transforms take up to 32 rows (8 for RMSNorm); M = %lld",
                 static_cast<long long>(p->M));
+  if (p->M > 32 && p->epilogue == B200_QMM_OUT_F32)
+    return Fail(B200_UNIMPLEMENTED, "b200_qmm: above 32 rows the output is bf16, bf16 + residual, or raw f32");
   if (p->N > INT32_MAX / 2 || p->K > INT32_MAX / 2) return Fail(B200_UNIMPLEMENTED, "b200_qmm: size exceeds int32");
   if (p->K % kGroupK != 0)
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: K = %lld is not a multiple of 64", static_cast<long long>(p->K));
@@ -1284,6 +1287,12 @@ b200_status b200_qmm_validate(const b200_qmm_params* p) { return Validate(p); }
 b200_status b200_qmm_plan(const b200_qmm_params* p, int* rows_per_cta, int* split_k, int* batch_blocks) {
   b200_status s = Validate(p);
   if (s != B200_OK) return s;
+  if (p->M > 32) {   // not the streaming kernel: panel-wise dequantisation + GEMM
+    if (rows_per_cta) *rows_per_cta = 0;
+    if (split_k) *split_k = 0;
+    if (batch_blocks) *batch_blocks = static_cast<int>(CeilDiv(p->M, 8));
+    return B200_OK;
+  }
   Plan pl;
   s = MakePlan(p, 148, 227 * 1024, &pl);
   if (s != B200_OK) return s;
@@ -1301,12 +1310,29 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
 
 namespace b200 {
 
+static bool TcRouteEnabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200_QMM_TC");
+    return v != nullptr && v[0] == '1';
+  }();
+  return on;
+}
+
 b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_params* p, const QmmTp* tp) {
   b200_status s = BeginLaunch(ctx);
   if (s != B200_OK) return s;
   s = Validate(p);
   if (s != B200_OK) return s;
   if (p->M == 0 || p->N == 0) return B200_OK;
+  // int4 in groups of 64, up to 8 rows: the tcgen05 route on request (b200_qmm_force_route 2, or B200_QMM_TC=1);
+  // measured slower than the mma.sync kernel at these batch sizes, see qmm_tc.cu
+  if (p->M > 32) {   // prefill-sized batches: dequantise into an L2-resident panel, then the tensor-core GEMM
+    if (tp != nullptr && tp->world > 1) return Fail(B200_UNIMPLEMENTED, "b200_qmm: the exchange takes up to 8 rows");
+    return QmmManyRows(ctx, stream, p);
+  }
+  const int forced = ctx->qmm_route.load();
+  if ((tp == nullptr || tp->world <= 1) && (forced == 2 || (forced == 0 && TcRouteEnabled())) && QmmTcEligible(ctx, p))
+    return QmmTcRun(ctx, stream, p);
   Plan pl;
   s = MakePlan(p, ctx->sm_count, ctx->max_smem_optin, &pl);
   if (s != B200_OK) return s;

@@ -115,7 +115,11 @@ def test_qmm_validate_and_plan():
     v = lambda s: lib.b200_qmm_validate(C.byref(s))
     assert v(q()) == L.OK
     assert v(q(bits=5)) == L.INVALID_ARGUMENT
-    assert v(q(M=33)) == L.UNIMPLEMENTED            # beyond the streaming kernel: dequantise + GEMM
+    assert v(q(M=33)) == L.OK                       # beyond the streaming kernel: panel-wise dequantise + GEMM
+    assert v(q(M=33, epi=2)) == L.UNIMPLEMENTED     # ... which has no "bf16-rounded value in f32" output
+    s33 = q(M=33)
+    s33.prologue = 2
+    assert v(s33) == L.UNIMPLEMENTED                # ... and fuses no input transform
     assert v(q(K=4000)) == L.UNIMPLEMENTED
     assert v(q(group=32)) == L.UNIMPLEMENTED
     assert v(q(bits=8, group=4096)) == L.OK         # per output channel

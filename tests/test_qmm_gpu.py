@@ -174,9 +174,12 @@ def test_edge_cases():
     n0 = p.default_context().launch_count
     out = p.qwen3.linear(dev(x)[:0], w)
     assert out.shape == (0, 37) and p.default_context().launch_count == n0
-    # too many rows: refused, not wrong
+    # more than 32 rows with a fused input transform: refused, not wrong
     with pytest.raises(p.B200Error) as e:
-        p.qwen3.linear(torch.zeros((33, 64), dtype=torch.bfloat16, device="cuda"), w)
+        p.qwen3.linear(torch.zeros((33, 128), dtype=torch.bfloat16, device="cuda"), w, silu_mul=True)
+    assert e.value.status == p._lib.UNIMPLEMENTED
+    with pytest.raises(p.B200Error) as e:
+        p.qwen3.linear(torch.zeros((33, 64), dtype=torch.bfloat16, device="cuda"), w, out_f32=True)
     assert e.value.status == p._lib.UNIMPLEMENTED
     assert p.default_context().error() == 0
 
@@ -238,3 +241,46 @@ def test_fused_silu_mul_prologue(m):
     want = quant.qmm(act, quant.bl_unpack_int4(packed), s, b, np.float32)
     got = host(p.qwen3.linear(dev(gu), _w4(packed, s, b), silu_mul=True)).astype(np.float32)
     assert got.shape == (m, n) and rel_rms_err(got, want) <= TOL
+
+
+@pytest.mark.parametrize("m", [33, 64, 128, 512])
+@pytest.mark.parametrize("fmt", ["int4", "int4_split_half", "int8_g64", "int8_channel", "bf16"])
+def test_many_rows_go_through_dequantise_and_gemm(m, fmt):
+    """More than 32 rows of x: panel-wise dequantisation into the L2-resident workspace + tensor-core
+    GEMM, for every weight format, against the oracle; one shape spans several panels."""
+    import torch
+    p = pkg()
+    k, n = (4096, 9000) if (fmt == "int4" and m == 64) else (1024, 520)   # 9000 rows x 4096: three panels, ragged tail
+    rng = np.random.default_rng(m)
+    x = rng.standard_normal((m, k), dtype=np.float32).astype(bf16)
+    w = (0.02 * rng.standard_normal((n, k), dtype=np.float32))
+    if fmt == "int4":
+        packed, s, b = quant.bl_quantize_int4(w)
+        wd, q = _w4(packed, s, b), quant.bl_unpack_int4(packed)
+    elif fmt == "int4_split_half":
+        pk, s3, b3 = quant.ref_quantize_int4(w)
+        s, b = s3[..., 0].astype(bf16), b3[..., 0].astype(bf16)
+        wd = {"q4h": dev(pk), "s": dev(s), "b": dev(b)}
+        q = quant.ref_unpack_int4(pk).reshape(n, k)
+    elif fmt.startswith("int8"):
+        q, s = quant.bl_quantize_int8(w, 64 if fmt == "int8_g64" else None)
+        b = None
+        wd = {"q": dev(q), "s": dev(s)}
+    else:
+        wm = w.astype(bf16)
+        wd = dev(wm)
+    if fmt == "bf16":
+        want = x.astype(np.float64) @ wm.astype(np.float64).T
+    else:
+        cols = np.random.default_rng(0).choice(n, 256, replace=False)
+        want = quant.qmm(x, q[cols], s[cols], None if b is None else b[cols], np.float32)
+    got = host(p.qwen3.linear(dev(x), wd)).astype(np.float32)
+    torch.cuda.synchronize()
+    assert got.shape == (m, n) and np.isfinite(got).all()
+    assert rel_rms_err(got if fmt == "bf16" else got[:, cols], want) <= TOL
+    if fmt == "int4":
+        res = rng.standard_normal((m, n), dtype=np.float32).astype(bf16)
+        got_r = host(p.qwen3.linear(dev(x), wd, residual=dev(res))).astype(np.float32)
+        want_r = res.astype(np.float32)[:, cols] + want
+        assert rel_rms_err(got_r[:, cols], want_r) <= TOL
+    assert p.default_context().error() == 0
