@@ -3,12 +3,18 @@
 // emitters produce them from examples/llm/qwen3.py:294-297,325 and
 // bench/jax_bench.py:44-46); this is one hand-written family.
 //
-// One pass over HBM: a row is read once with 16-byte loads into shared memory
-// as f32 while the first statistic is accumulated, the second statistic and
+// One pass over HBM.  Rows whose length is 32, 128, ... 1024 threads times 1, 2, 4 or 8
+// 16-byte vectors (every shape of the benchmark configurations) stay in REGISTERS: all
+// loads of a row are issued before the first is used, the statistics come from the
+// registers (shuffles within a warp, one exchange through shared memory for a CTA per
+// row), and the row is written once.  Other rows: a row is read once with 16-byte loads
+// into shared memory as f32 while the first statistic is accumulated, the second statistic and
 // the output come from shared memory, and the row is written once.  Short rows
 // get a warp each (several rows per CTA, shuffle reductions only), long rows a
 // CTA each; rows that do not fit shared memory fall back to re-reading global
 // memory (L2-resident at those sizes).  Statistics are f32.
+#include <type_traits>
+
 #include "common.cuh"
 
 using namespace b200;
@@ -214,6 +220,91 @@ __global__ void rownorm_block_kernel(const RowArgs a) {
   }
 }
 
+// Register-resident rows: n == threads-per-row * NV * (16 / sizeof(T)).  WARP: a warp per row,
+// eight rows per CTA; else the whole CTA on one row.
+template <typename T, int KIND, int NV, bool WARP>
+__global__ void __launch_bounds__(WARP ? 256 : 1024) rownorm_reg_kernel(const RowArgs a) {
+  constexpr int V = Vec<T>::kN;
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tpr = WARP ? 32 : static_cast<int>(blockDim.x);
+  const int t = WARP ? static_cast<int>(threadIdx.x & 31) : static_cast<int>(threadIdx.x);
+  const int wpb = blockDim.x >> 5;
+  const int64_t row0 = WARP ? static_cast<int64_t>(blockIdx.x) * wpb + (threadIdx.x >> 5) : blockIdx.x;
+  const int64_t rstride = WARP ? static_cast<int64_t>(gridDim.x) * wpb : gridDim.x;
+  const T* gain = static_cast<const T*>(a.gain);
+  const T* beta = static_cast<const T*>(a.beta);
+  for (int64_t row = row0; row < a.rows; row += rstride) {
+    const T* x = static_cast<const T*>(a.x) + row * a.n;
+    T* y = static_cast<T*>(a.y) + row * a.n;
+    float v[NV][V];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) load_vec<T>(x + (j * tpr + t) * V, v[j]);
+    float st = (KIND == kSoftmax || KIND == kLogSoftmax) ? -INFINITY : 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        if (KIND == kRms) st = fmaf(v[j][e], v[j][e], st);
+        else if (KIND == kLayerNorm) st += v[j][e];
+        else st = nan_max(st, v[j][e]);
+      }
+    if (KIND == kSoftmax || KIND == kLogSoftmax) st = group_nanmax<WARP>(st, scratch);
+    else st = group_sum<WARP>(st, scratch);
+    float scale = 1.0f, shift = 0.0f;
+    if (KIND == kRms) {
+      scale = 1.0f / sqrtf(st / static_cast<float>(a.n) + a.eps);
+    } else if (KIND == kLayerNorm) {
+      const float mean = st / static_cast<float>(a.n);
+      float sq = 0.0f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float d = v[j][e] - mean;
+          sq = fmaf(d, d, sq);
+        }
+      sq = group_sum<WARP>(sq, scratch);
+      scale = 1.0f / sqrtf(sq / static_cast<float>(a.n) + a.eps);
+      shift = mean;
+    } else {
+      float sum = 0.0f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float ex = expf(v[j][e] - st);
+          if (KIND == kSoftmax) v[j][e] = ex;
+          sum += ex;
+        }
+      sum = group_sum<WARP>(sum, scratch);
+      if (KIND == kSoftmax) scale = sum;   // divide, like the reference (not multiply by 1/sum)
+      else { shift = st; scale = logf(sum); }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = (j * tpr + t) * V;
+      float g[V], bt[V], o[V];
+      if (KIND == kRms || (KIND == kLayerNorm && gain != nullptr)) load_vec<T>(gain + i, g);
+      if (KIND == kLayerNorm && beta != nullptr) load_vec<T>(beta + i, bt);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        if (KIND == kRms) o[e] = (v[j][e] * scale) * g[e];
+        else if (KIND == kSoftmax) o[e] = v[j][e] / scale;
+        else if (KIND == kLogSoftmax) o[e] = (v[j][e] - shift) - scale;
+        else {
+          float r = (v[j][e] - shift) * scale;
+          if (gain != nullptr) r *= g[e];
+          if (beta != nullptr) r += bt[e];
+          o[e] = r;
+        }
+      }
+      store_vec<T>(y + i, o);
+    }
+  }
+}
+
 // Rows too long for shared memory: statistics by re-reading global memory.
 template <typename T, int KIND>
 __global__ void rownorm_long_kernel(const RowArgs a) {
@@ -282,6 +373,33 @@ b200_status LaunchRows(b200_context* ctx, cudaStream_t stream, const RowArgs& a)
   lc.stream = stream;
   lc.pdl = true;
   cudaError_t e;
+  // register-resident rows (f32 and bf16): threads per row x vectors per thread == vectors per row
+  if (!std::is_same<T, __half>::value && vec && (a.gain == nullptr || Aligned(a.gain, 16)) && (a.beta == nullptr || Aligned(a.beta, 16))) {
+    const int vecs = a.n / V;
+    int tpr = 0, nv = 0;
+    for (int cand : {8, 4, 2, 1})
+      if (tpr == 0 && vecs == 32 * cand) { tpr = 32; nv = cand; }
+    for (int cand : {8, 4, 2, 1})
+      for (int th : {128, 256, 512, 1024})
+        if (tpr == 0 && vecs == th * cand) { tpr = th; nv = cand; }
+    if (tpr != 0) {
+      const bool warp = tpr == 32;
+      lc.block = dim3(warp ? 256 : tpr);
+      lc.grid = dim3(static_cast<unsigned>(warp ? std::min<int64_t>(CeilDiv(a.rows, 8), ctx->sm_count * 8)
+                                                : std::min<int64_t>(a.rows, static_cast<int64_t>(ctx->sm_count) * std::max(1, 2048 / tpr))));
+#define B200_ROW_CASE(NVV)                                                                                         \
+  case NVV: e = warp ? Launch(lc, rownorm_reg_kernel<T, KIND, NVV, true>, a) : Launch(lc, rownorm_reg_kernel<T, KIND, NVV, false>, a); break;
+      switch (nv) {
+        B200_ROW_CASE(8)
+        B200_ROW_CASE(4)
+        B200_ROW_CASE(2)
+        default: e = warp ? Launch(lc, rownorm_reg_kernel<T, KIND, 1, true>, a) : Launch(lc, rownorm_reg_kernel<T, KIND, 1, false>, a); break;
+      }
+#undef B200_ROW_CASE
+      if (e != cudaSuccess) return Stick(ctx, Fail(B200_INTERNAL, "b200_rownorm launch: %s", cudaGetErrorString(e)));
+      return EndLaunch(ctx, "b200_rownorm");
+    }
+  }
   if (a.n <= 2048) {
     // a warp per row; 8 warps per CTA
     const int wpb = 8;

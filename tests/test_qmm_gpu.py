@@ -284,3 +284,73 @@ def test_many_rows_go_through_dequantise_and_gemm(m, fmt):
         want_r = res.astype(np.float32)[:, cols] + want
         assert rel_rms_err(got_r[:, cols], want_r) <= TOL
     assert p.default_context().error() == 0
+
+
+@pytest.mark.parametrize("m", [1, 8, 32])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 12288), (12288, 4096)])
+def test_int8_per_channel_product_qwen3_shapes(m, k, n):
+    """The int8 per-channel products of the benchmark configuration at full size (a sample of 512
+    output channels is checked on the CPU)."""
+    p = pkg()
+    x, q, s, _ = inputs.config3(m, k, n)
+    got = host(p.qwen3.linear(dev(x), {"q": dev(q), "s": dev(s)})).astype(np.float32)
+    cols = np.random.default_rng(1).choice(n, 512, replace=False)
+    want = quant.qmm(x, q[cols], s[cols], None, np.float32)
+    assert rel_rms_err(got[:, cols], want) <= TOL
+    assert np.isfinite(got).all()
+
+
+def _one_hot_check(p, wd, dense, k, ks, m):
+    """x row i = e_{ks[i]} (the other rows of the batch zero): the product is column ks[i] of the
+    dequantised matrix, to the one bf16 rounding of the output."""
+    x = np.zeros((m, k), np.float32)
+    for i, kk in enumerate(ks):
+        x[i, kk] = 1.0
+    got = host(p.qwen3.linear(dev(x.astype(bf16)), wd)).astype(np.float32)
+    want = np.zeros((m, dense.shape[0]), np.float32)
+    want[:len(ks)] = dense[:, ks].T
+    ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want), 1e-30))) - 7)
+    assert np.all(np.abs(got - want) <= 0.51 * ulp + 1e-6)
+
+
+@pytest.mark.parametrize("m", [9, 17, 32])
+@pytest.mark.parametrize("k", [4096, 12288])
+def test_int4_one_hot_unpack_at_every_batch_block(m, k):
+    """The nibble order and the k mapping of every batch-block variant (two, three and four blocks
+    of 8 rows), K = 4096 and K = 12288 (the K-split forms): positions inside a word, across words,
+    groups, copy chunks and K slices."""
+    p = pkg()
+    n = 1024
+    _, packed, s, b, _ = inputs.config4(1, k, n)
+    ks = [0, 1, 6, 7, 8, 63, 64, 65, 511, 512, 2047, 2048, k // 2 - 1, k // 2, k - 65, k - 64, k - 1][:m]
+    dense = quant.dequant_f32(quant.bl_unpack_int4(packed), s, b)
+    _one_hot_check(p, _w4(packed, s, b), dense, k, ks, m)
+
+
+@pytest.mark.parametrize("m", [1, 8, 17])
+def test_int4_split_half_one_hot_unpack(m):
+    """The reference's split-half byte layout (element j in the low nibble of byte j, element j + 32
+    in the high nibble) through the product kernel."""
+    p = pkg()
+    k, n = 4096, 512
+    rng = np.random.default_rng(12)
+    w = 0.02 * rng.standard_normal((n, k), dtype=np.float32)
+    pk, s3, b3 = quant.ref_quantize_int4(w)
+    s, b = s3[..., 0].astype(bf16), b3[..., 0].astype(bf16)
+    wd = {"q4h": dev(pk), "s": dev(s), "b": dev(b)}
+    dense = quant.dequant_f32(quant.ref_unpack_int4(pk).reshape(n, k), s, b)
+    ks = [0, 1, 31, 32, 33, 63, 64, 95, 96, 127, 2048, 2079, 2080, 4032, 4063, 4064, 4095][:m]
+    _one_hot_check(p, wd, dense, k, ks, m)
+
+
+@pytest.mark.parametrize("group", [None, 64])
+@pytest.mark.parametrize("m,k", [(1, 4096), (8, 12288), (17, 4096), (32, 12288)])
+def test_int8_one_hot_unpack(group, m, k):
+    p = pkg()
+    n = 512
+    rng = np.random.default_rng(13)
+    w = 0.02 * rng.standard_normal((n, k), dtype=np.float32)
+    q, s = quant.bl_quantize_int8(w, group)
+    dense = quant.dequant_f32(q, s, None, group or k)
+    ks = [0, 1, 15, 16, 63, 64, 127, 128, 1023, 1024, 2047, 2048, k // 2, k - 129, k - 128, k - 64, k - 1][:m]
+    _one_hot_check(p, {"q": dev(q), "s": dev(s)}, dense, k, ks, m)
