@@ -103,6 +103,7 @@ struct QmmArgs {
   uint32_t* tp_done;                     // CTAs of the pushing kernel that have finished
   const uint2* tp_src;                   // prologue: slot 0 of the lines in this rank's memory, [world][cap]
   long long tp_cap;                      // floats per sub-slot; a slot is world sub-slots
+  int tp_nowait;                         // measurement only (B200_TP_NOWAIT=1): take the lines as they are (wrong results, no waiting)
   __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
 };
 
@@ -120,34 +121,50 @@ __device__ __forceinline__ uint4 ld_lines2(const uint2* p) {
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
-// Eight consecutive lines of exchange n (p 16-byte aligned).  Waits, bounded, for lines that have not
-// landed yet; once any wait of this context has run out (the status word is set) nobody waits again.
-// false: the values are not the peers' (zeros are returned).
-__device__ __forceinline__ bool ld_lines8(const uint2* p, uint32_t n, int* status, int where, float* out) {
-  uint4 v[4];
+// Eight consecutive lines of exchange n from each of R ranks' sub-slots (p 16-byte aligned, `pitch`
+// lines between sub-slots), added to sum[] in rank order.  All R x 4 loads are in flight together
+// (one trip to L2 for R ranks).  Waits, bounded, for lines that have not landed yet; once any wait
+// of this context has run out (the status word is set) nobody waits again and the missing values
+// count as zero.
+template <int R>
+__device__ __forceinline__ void add_lines8(const uint2* p, size_t pitch, uint32_t n, int* status, int where, float (&sum)[8],
+                                           bool nowait) {
+  uint4 v[R][4];
   long long t0 = 0;
   bool ok;
   for (;;) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = ld_lines2(p + 2 * j);
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[r][j] = ld_lines2(p + r * pitch + 2 * j);
     ok = true;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) ok = ok && v[j].y == n && v[j].w == n;
-    if (ok) break;
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ok = ok && v[r][j].y == n && v[r][j].w == n;
+    if (ok || nowait) break;
     if (*reinterpret_cast<volatile int*>(status) != 0) break;
     if (t0 == 0) {
       t0 = clock64();
     } else if (clock64() - t0 > 4000000000ll) {
-      report_timeout(status, where);
+      int late = 0;   // the first rank whose lines are missing
+#pragma unroll
+      for (int r = R - 1; r >= 0; --r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v[r][j].y != n || v[r][j].w != n) late = r;
+      report_timeout(status, where + late);
       break;
     }
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    out[2 * j] = ok ? __uint_as_float(v[j].x) : 0.0f;
-    out[2 * j + 1] = ok ? __uint_as_float(v[j].z) : 0.0f;
-  }
-  return ok;
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool have = v[r][j].y == n && v[r][j].w == n;
+      sum[2 * j] += have ? __uint_as_float(v[r][j].x) : 0.0f;
+      sum[2 * j + 1] += have ? __uint_as_float(v[r][j].z) : 0.0f;
+    }
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -481,13 +498,12 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       if (TP && tp_slot != nullptr) {
         float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
         const uint2* base = tp_slot + static_cast<size_t>(m) * a.K + k;
+        // rank order on every rank: identical sums everywhere; two ranks' lines per trip to L2
+        const size_t pitch = static_cast<size_t>(a.tp_cap);
+        int r = 0;
 #pragma unroll 1
-        for (int r = 0; r < a.tp_world; ++r) {   // rank order on every rank: identical sums everywhere
-          float part[8];
-          ld_lines8(base + static_cast<size_t>(r) * a.tp_cap, tp_n, a.status, 400 + r, part);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) sum[j] += part[j];
-        }
+        for (; r + 2 <= a.tp_world; r += 2) add_lines8<2>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
+        if (r < a.tp_world) add_lines8<1>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
 #pragma unroll
         for (int j = 0; j < 8; ++j) dst[j] = bf16_round(dst[j] + bf16_round(sum[j]));
       }
@@ -1102,7 +1118,11 @@ b200_status MakePlanImpl(const b200_qmm_params* p, int sm_count, int max_smem, P
   for (int split = 1; split <= 8 && !found; split <<= 1) {
     if (K % (split * kGroupK) != 0) break;
     const int kc = K / split;
-    const bool fills = static_cast<int64_t>(pl.tiles) * split >= sm_count;
+    // Up to 8 rows of x a fifth of the SMs is "enough": measured at M = 1, 1536 x 4096 takes 3.7 us on 96 CTAs
+    // against 8.4 us as 96 clusters of two, 768 x 4096 3.3 us on 48 CTAs against 8.8 us as clusters of four
+    // (the exchange through distributed shared memory costs more than the idle SMs).
+    const int fill_pct = pl.mb == 1 ? 20 : 100;
+    const bool fills = static_cast<int64_t>(pl.tiles) * split * 100 >= static_cast<int64_t>(sm_count) * fill_pct;
     const bool last = split == 8 || K % (2 * split * kGroupK) != 0;
     const bool tall = pl.rt > pl.mb;   // the two-tile variant never splits K
     if (static_cast<size_t>(M) * kc * 2 > x_budget || !(fills || last || tall)) continue;
@@ -1370,6 +1390,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   a.tp_count = a.tp_done = nullptr;
   a.tp_src = nullptr;
   a.tp_cap = 0;
+  a.tp_nowait = 0;
   a.x_out = nullptr;
   for (int r = 0; r < kTpMaxWorld; ++r) {
     a.tp_dst[r] = nullptr;
@@ -1395,6 +1416,8 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
       if (p->prologue != B200_QMM_PRO_RMSNORM || !a.x_vec || a.ldx != a.K || a.K % 8 != 0 || p->M * p->K > tp->cap)
         return Fail(B200_INVALID_ARGUMENT, "b200_qmm: summing the ranks' partial sums goes with the RMSNorm prologue on dense, aligned rows");
       a.tp_src = tp->src;
+      static const bool nowait = std::getenv("B200_TP_NOWAIT") != nullptr;
+      a.tp_nowait = nowait ? 1 : 0;
       a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
     }
   }

@@ -133,7 +133,8 @@ def test_qmm_validate_and_plan():
     plan = p.qwen3.qmm_plan
     assert plan(1, 4096, 4096) == (32, 1, 1)       # one 32-row tile for 128 CTAs costs the busiest SM what two 16-row tiles would
     assert plan(1, 6144, 4096) == (32, 1, 1) and plan(1, 2048, 4096)[0] == 16
-    assert plan(1, 1024, 4096)[1] >= 4
+    assert plan(1, 1024, 4096)[1] == 1              # 64 CTAs without a K split beat 64 clusters of four (measured)
+    assert plan(1, 256, 4096)[1] >= 2               # a handful of tiles: K is split across a cluster
     assert plan(8, 4096, 4096) == (16, 1, 1)        # persistent CTAs stage x once: no need for taller tiles
     assert plan(16, 4096, 4096)[0] == 32 and plan(16, 4096, 4096)[2] == 2
     r32, s32, mb32 = plan(32, 4096, 12288)
