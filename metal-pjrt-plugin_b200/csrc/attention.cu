@@ -421,6 +421,17 @@ b200_status StaticScratch(b200_context* ctx, float** out) {
 
 }  // namespace
 
+namespace b200 {
+// Called by b200_context_create: the address of the built-in scratch is looked up while the
+// context is made, so that b200_attention_decode_static itself never calls into the runtime
+// for it (it may run inside a stream capture).
+b200_status AttnStaticScratchInit(b200_context* ctx) {
+  if (ctx->device < 0 || ctx->device >= kMaxDevices) return B200_OK;   // (the static entry point refuses such a device itself)
+  float* p = nullptr;
+  return StaticScratch(ctx, &p);
+}
+}  // namespace b200
+
 extern "C" {
 
 size_t b200_attention_scratch_bytes(int64_t batch, int heads, int head_dim, int64_t max_len) {

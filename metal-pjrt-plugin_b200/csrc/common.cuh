@@ -50,6 +50,8 @@ void SetError(const char* fmt, ...);
 b200_status Fail(b200_status code, const char* fmt, ...);
 // Records `code` as the context's sticky error (first one wins) and returns it.
 b200_status Stick(b200_context* ctx, b200_status code);
+// attention.cu: caches the device address of the built-in attention scratch for this context's device.
+b200_status AttnStaticScratchInit(b200_context* ctx);
 // Called by every entry point before it enqueues: returns the sticky error if
 // one is set, applies host-side fault injection, makes the device current.
 b200_status BeginLaunch(b200_context* ctx);

@@ -149,6 +149,10 @@ b200_status b200_context_create(int device_ordinal, b200_context** out) {
     return s;
   }
   ctx->host_status[0] = 0;
+  if (AttnStaticScratchInit(ctx) != B200_OK) {
+    b200_context_destroy(ctx);
+    return B200_INTERNAL;
+  }
   *out = ctx;
   return B200_OK;
 }
