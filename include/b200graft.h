@@ -70,6 +70,13 @@ void b200_context_fail_launch_after(b200_context* ctx, int64_t n);
  * its wait id (900) to the status word and returns.  After the stream is synchronised
  * b200_context_error turns sticky B200_TIMEOUT; other contexts are unaffected. */
 b200_status b200_context_wait_probe(b200_context* ctx, b200_stream stream, int64_t limit_cycles);
+/* Measurement only: the cost of one tcgen05.mma.  One CTA issues `count` (<= 4096) instructions of
+ * kind 0 (kind::f8f6f4, e4m3 operands) or 1 (kind::f16, bf16) with the given M (64, 128) and N, A from
+ * tensor memory (1) or shared memory (0), cycling over `accumulators` (1..8) D regions, then commits
+ * and waits (bounded).  cycles_device[0] = SM cycles spent issuing, [1] = until the commit arrived
+ * (int64, device memory).  `opbench.py umma` prints the table. */
+b200_status b200_probe_umma_rate(b200_context* ctx, b200_stream stream, int kind, int m, int n, int a_from_tmem,
+                                 int accumulators, int count, int64_t* cycles_device);
 /* Number of kernels this context has enqueued so far. */
 int64_t b200_context_launch_count(b200_context* ctx);
 

@@ -108,6 +108,7 @@ PROTOTYPES = {
     "b200_gemm_work": (C.c_uint64, [C.POINTER(GemmParamsC)]),
     "b200_gemm_force_route": (None, [_VP, _I]),
     "b200_qmm_force_route": (None, [_VP, _I]),
+    "b200_probe_umma_rate": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _I, _VP]),
     "b200_decode_epilogue": (_I, [C.c_int32, C.POINTER(EpilogueSpecC)]),
     "b200_matmul_plan_create": (_I, [C.POINTER(MatmulConfigC), C.c_int32, C.POINTER(MatmulPlanC)]),
     "b200_matmul_execute": (_I, [_VP, _VP, C.POINTER(MatmulPlanC), _VP, _VP, _VP, _VP, _VP, _VP, C.c_size_t, C.c_size_t,

@@ -7,6 +7,7 @@ time; JSON lines).  Also the small cases the ncu summaries under profiles/ come 
     python opbench.py gemm --m 2048 --n 4096 --k 4096 [--act 3] [--bias]
     python opbench.py rows --kind softmax --rows 8192 --n 1024 [--dtype f32]
     python opbench.py sweep          # the benchmark configs 2-4
+    python opbench.py umma           # SM cycles per tcgen05.mma by shape
 """
 import argparse
 import json
@@ -141,7 +142,7 @@ def bench_rows(pkg, kind, rows, n, dtype, reps, buffers=4):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["qmm", "gemm", "rows", "sweep"])
+    ap.add_argument("op", choices=["qmm", "gemm", "rows", "sweep", "umma"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--group", type=int, default=64, help="int8: 64, or 0 for per-channel")
     ap.add_argument("--m", type=int, default=1)
@@ -165,6 +166,22 @@ def main():
     elif a.op == "gemm":
         print(json.dumps(bench_gemm(pkg, a.m, a.n, a.k, a.act, a.bias, a.reps, a.dtype, a.tb,
                                     max(4, min(a.buffers, int(512e6 // (a.n * a.k * 2)))), a.route)), flush=True)
+    elif a.op == "umma":
+        # SM cycles per tcgen05.mma by shape (b200_probe_umma_rate): 256 instructions from one thread
+        import torch
+        from metal_pjrt_plugin_b200 import _lib
+        ctx = pkg.default_context()
+        out = torch.zeros(2, dtype=torch.int64, device="cuda")
+        for kind, m, n, at, nd in [(0, 128, 16, 1, 1), (0, 128, 16, 1, 8), (0, 128, 16, 0, 8), (0, 128, 64, 1, 1), (0, 128, 256, 1, 1),
+                                   (0, 128, 256, 0, 1), (0, 64, 8, 1, 8), (0, 64, 16, 0, 8), (1, 128, 16, 1, 8), (1, 128, 16, 0, 8),
+                                   (1, 128, 256, 0, 1), (1, 64, 8, 0, 8)]:
+            for _ in range(2):
+                _lib.check(pkg.lib().b200_probe_umma_rate(ctx.handle, _lib.current_stream(), kind, m, n, at, nd, 256, out.data_ptr()))
+            torch.cuda.synchronize()
+            issue, done = (int(v) for v in out.tolist())
+            print(json.dumps({"op": "umma", "kind": "f8f6f4" if kind == 0 else "f16", "m": m, "n": n,
+                              "a": "tmem" if at else "smem", "accumulators": nd, "cycles_per_mma_issue": issue / 256,
+                              "cycles_per_mma_complete": done / 256}), flush=True)
     elif a.op == "rows":
         print(json.dumps(bench_rows(pkg, a.kind, a.rows, a.n, a.dtype, a.reps)), flush=True)
     else:

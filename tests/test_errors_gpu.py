@@ -81,3 +81,20 @@ def test_a_bounded_wait_that_runs_out_turns_into_a_sticky_timeout():
     assert lib.b200_context_wait_probe(fresh.handle, L.current_stream(), 0) == L.INVALID_ARGUMENT
     fresh.close()
     ctx.close()
+
+
+def test_umma_rate_probe_runs_and_reports_a_sane_cost():
+    """The tcgen05.mma cost probe: runs, leaves the status word clean, and gives a per-instruction
+    cost of the order the design notes quote (about 194 cycles; anything from 16 to 2000 passes,
+    the test is about the plumbing, the number is for opbench)."""
+    import torch
+    p = pkg()
+    ctx = p.Context(0)
+    out = torch.zeros(2, dtype=torch.int64, device="cuda")
+    for kind, m, n, at, nd in [(0, 128, 16, 1, 2), (1, 128, 256, 0, 1), (0, 64, 8, 0, 8)]:
+        p._lib.check(p.lib().b200_probe_umma_rate(ctx.handle, p._lib.current_stream(), kind, m, n, at, nd, 128, out.data_ptr()))
+        torch.cuda.synchronize()
+        issue, done = (int(v) for v in out.tolist())
+        assert 16 * 128 <= done <= 2000 * 128 and issue <= done
+    assert ctx.error() == 0
+    assert p.lib().b200_probe_umma_rate(ctx.handle, p._lib.current_stream(), 0, 128, 24, 1, 1, 16, out.data_ptr()) == p._lib.INVALID_ARGUMENT
