@@ -246,9 +246,11 @@ def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
     x_gu = torch.randn((batch, 2 * I), device=device).to(bf)
     res = torch.randn((batch, E), device=device).to(bf)
     gain = torch.ones((E,), device=device, dtype=bf)
-    forms = {"qkv": lambda w: pkg.qwen3.linear(x_e, w, rms_gain=gain, ctx=ctx),
+    # (above 8 rows the decoder runs the RMSNorm as a kernel of its own, so the projection is launched plain)
+    norm = dict(rms_gain=gain) if batch <= 8 else {}
+    forms = {"qkv": lambda w: pkg.qwen3.linear(x_e, w, ctx=ctx, **norm),
              "o": lambda w: pkg.qwen3.linear(x_hd, w, residual=res, ctx=ctx),
-             "gate_up": lambda w: pkg.qwen3.linear(x_e, w, rms_gain=gain, ctx=ctx),
+             "gate_up": lambda w: pkg.qwen3.linear(x_e, w, ctx=ctx, **norm),
              "down": lambda w: pkg.qwen3.linear(x_gu, w, silu_mul=True, residual=res, ctx=ctx)}
     jobs, nbytes = [], 0
     for lp in params["layers"]:
