@@ -103,7 +103,8 @@ struct QmmArgs {
   uint32_t* tp_done;                     // CTAs of the pushing kernel that have finished
   const uint2* tp_src;                   // prologue: slot 0 of the lines in this rank's memory, [world][cap]
   long long tp_cap;                      // floats per sub-slot; a slot is world sub-slots
-  int tp_nowait;                         // measurement only (B200_TP_NOWAIT=1): take the lines as they are (wrong results, no waiting)
+  int tp_nowait;                         // measurement only, wrong results: B200_TP_NOWAIT=1 take the lines as they are (no waiting),
+                                         // =2 do not read them at all, =4 (pusher) store to this rank's own memory only
   __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
 };
 
@@ -291,7 +292,7 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
     const size_t so_ = static_cast<size_t>(n_x & 1u) * a.tp_world * a.tp_cap + o;
 #pragma unroll
     for (int r = 0; r < kTpMaxWorld; ++r)
-      if (r < a.tp_world) st_line(a.tp_dst[r] + so_, v, n_x);
+      if (r < a.tp_world && (a.tp_nowait != 4 || r == a.tp_rank)) st_line(a.tp_dst[r] + so_, v, n_x);
     return;
   }
   if (a.epilogue == B200_QMM_OUT_F32_RAW) {
@@ -502,6 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         const size_t pitch = static_cast<size_t>(a.tp_cap);
         int r = 0;
 #pragma unroll 1
+        if (a.tp_nowait == 2) r = a.tp_world;
         for (; r + 2 <= a.tp_world; r += 2) add_lines8<2>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
         if (r < a.tp_world) add_lines8<1>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
 #pragma unroll
@@ -1330,6 +1332,14 @@ b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_p
 
 namespace b200 {
 
+static int TpMeasureMode() {
+  static const int mode = [] {
+    const char* v = std::getenv("B200_TP_NOWAIT");
+    return v != nullptr ? atoi(v) : 0;
+  }();
+  return mode;
+}
+
 static bool TcRouteEnabled() {
   static const bool on = [] {
     const char* v = std::getenv("B200_QMM_TC");
@@ -1409,6 +1419,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
         return Fail(B200_INVALID_ARGUMENT, "b200_qmm: pushed partial sums are dense raw f32");
       a.epilogue = kEpiloguePush;
       a.tp_done = tp->done;
+      a.tp_nowait = TpMeasureMode();
       for (int r = 0; r < tp->world; ++r) {
         a.tp_dst[r] = tp->dst[r];
       }
@@ -1416,8 +1427,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
       if (p->prologue != B200_QMM_PRO_RMSNORM || !a.x_vec || a.ldx != a.K || a.K % 8 != 0 || p->M * p->K > tp->cap)
         return Fail(B200_INVALID_ARGUMENT, "b200_qmm: summing the ranks' partial sums goes with the RMSNorm prologue on dense, aligned rows");
       a.tp_src = tp->src;
-      static const bool nowait = std::getenv("B200_TP_NOWAIT") != nullptr;
-      a.tp_nowait = nowait ? 1 : 0;
+      a.tp_nowait = TpMeasureMode();
       a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
     }
   }
