@@ -106,6 +106,8 @@ struct QmmArgs {
   int tp_nowait;                         // measurement only, wrong results: B200_TP_NOWAIT=1 take the lines as they are (no waiting),
                                          // =2 do not read them at all, =4 (pusher) store to this rank's own memory only
   __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
+  uint2* tp_bcast;                       // two-level sum: slot 0 of this rank's lines {two bf16 of the new residual, exchange number};
+                                         // null: every CTA sums the ranks' lines itself
 };
 
 constexpr int kEpilogueGemm = 100;
@@ -482,13 +484,72 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     // the exchange number is final; a peer's line that has not landed yet is read again (bounded).
     // Only this rank's own memory is ever read.
     const uint2* tp_slot = nullptr;
+    const uint2* tp_bc = nullptr;
     uint32_t tp_n = 0;
     if (TP && a.tp_src != nullptr) {
       tp_n = *a.tp_count;
       tp_slot = a.tp_src + static_cast<size_t>(tp_n & 1u) * a.tp_world * a.tp_cap;
+      if (a.tp_bcast != nullptr) {
+        // Two levels: the sum over ranks is formed ONCE per rank.  The row is cut into
+        // runs of 8 values that are dealt out over the CTAs of this kernel; the owner of a run adds the
+        // ranks' lines and the old residual, writes the new residual row, and publishes the 8 bf16 values
+        // as four {two values, exchange number} lines in this rank's own memory, where every CTA then
+        // reads the whole new row (K / 2 lines instead of world * K).  All CTAs of the grid are resident
+        // (one per SM), so waiting for a line another CTA of the grid publishes cannot deadlock; the wait
+        // is bounded like every other.
+        uint2* bc = a.tp_bcast + static_cast<size_t>(tp_n & 1u) * (a.tp_cap / 2);
+        tp_bc = bc;
+        const int n_ctas = static_cast<int>(gridDim.x * gridDim.y), cta_id = static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x);
+        const int runs = a.M * (a.K / 8);
+        const size_t pitch = static_cast<size_t>(a.tp_cap);
+        for (int run = cta_id * 8 + (tid & 7) + (tid >> 3) * n_ctas * 8; run < runs; run += (kConsumerThreads / 8) * n_ctas * 8) {
+          // (8 consecutive runs = 64 values per CTA and step, so a warp's quarter reads 512 contiguous bytes per rank)
+          const int m = run / (a.K / 8), k = (run % (a.K / 8)) * 8;
+          float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+          const uint2* base = tp_slot + static_cast<size_t>(m) * a.K + k;
+          int r = a.tp_nowait == 2 ? a.tp_world : 0;
+#pragma unroll 1
+          for (; r + 2 <= a.tp_world; r += 2) add_lines8<2>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
+          if (r < a.tp_world) add_lines8<1>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(m) * a.ldx + k));
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            o[j] = pack_bf16(bf16_lo(w[j]) + bf16_round(sum[2 * j]), bf16_hi(w[j]) + bf16_round(sum[2 * j + 1]));
+          if (a.x_out != nullptr) *reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(m) * a.K + k) = make_uint4(o[0], o[1], o[2], o[3]);
+          uint2* dst = bc + (static_cast<size_t>(m) * a.K + k) / 2;
+          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o[0]), "r"(tp_n), "r"(o[1]), "r"(tp_n) : "memory");
+          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(o[2]), "r"(tp_n), "r"(o[3]), "r"(tp_n) : "memory");
+        }
+      }
     }
     // eight values of row m starting at k, the partial sums folded in
     auto load_x8 = [&](int m, int k, float* dst) {
+      if (TP && tp_bc != nullptr) {   // the new residual row as this rank published it
+        const uint2* src = tp_bc + (static_cast<size_t>(m) * a.K + k) / 2;
+        uint4 v0, v1;
+        long long t0 = 0;
+        for (;;) {
+          v0 = ld_lines2(src);
+          v1 = ld_lines2(src + 2);
+          if ((v0.y == tp_n && v0.w == tp_n && v1.y == tp_n && v1.w == tp_n) || a.tp_nowait != 0) break;
+          if (*reinterpret_cast<volatile int*>(a.status) != 0) break;
+          if (t0 == 0) {
+            t0 = clock64();
+          } else if (clock64() - t0 > 4000000000ll) {
+            report_timeout(a.status, 450);
+            break;
+          }
+        }
+        const uint32_t w[4] = {v0.x, v0.z, v1.x, v1.z};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dst[2 * j] = bf16_lo(w[j]);
+          dst[2 * j + 1] = bf16_hi(w[j]);
+        }
+        return;
+      }
       const uint4 raw = __ldg(reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(m) * a.ldx + k));
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -501,9 +562,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         const uint2* base = tp_slot + static_cast<size_t>(m) * a.K + k;
         // rank order on every rank: identical sums everywhere; two ranks' lines per trip to L2
         const size_t pitch = static_cast<size_t>(a.tp_cap);
-        int r = 0;
+        int r = a.tp_nowait == 2 ? a.tp_world : 0;
 #pragma unroll 1
-        if (a.tp_nowait == 2) r = a.tp_world;
         for (; r + 2 <= a.tp_world; r += 2) add_lines8<2>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
         if (r < a.tp_world) add_lines8<1>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
 #pragma unroll
@@ -594,7 +654,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         if (TP && valid && tp_slot != nullptr) {
           load_x8(um, kbase + run0, e);
           load_x8(um, kbase + run1, e + 8);
-          if (blockIdx.x == 0 && a.x_out != nullptr) {   // the new residual row, once (each K slice by its CTA of tile 0)
+          if (blockIdx.x == 0 && a.x_out != nullptr && tp_bc == nullptr) {   // the new residual row, once (each K slice by its CTA of tile 0)
             __nv_bfloat16* xo = a.x_out + static_cast<size_t>(um) * a.K + kbase;
             *reinterpret_cast<uint4*>(xo + run0) = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
             *reinterpret_cast<uint4*>(xo + run1) = make_uint4(pack_bf16(e[8], e[9]), pack_bf16(e[10], e[11]), pack_bf16(e[12], e[13]), pack_bf16(e[14], e[15]));
@@ -1402,6 +1462,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   a.tp_cap = 0;
   a.tp_nowait = 0;
   a.x_out = nullptr;
+  a.tp_bcast = nullptr;
   for (int r = 0; r < kTpMaxWorld; ++r) {
     a.tp_dst[r] = nullptr;
   }
@@ -1429,6 +1490,8 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
       a.tp_src = tp->src;
       a.tp_nowait = TpMeasureMode();
       a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
+      static const int two_level = [] { const char* v = std::getenv("B200_TP_TWO_LEVEL"); return v != nullptr ? atoi(v) : -1; }();
+      if (tp->bcast != nullptr && two_level != 0) a.tp_bcast = tp->bcast;   // (B200_TP_TWO_LEVEL=0: every CTA sums the ranks' lines itself)
     }
   }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);

@@ -184,11 +184,14 @@ __global__ void __launch_bounds__(1024) peer_sum_residual_norm_kernel(const Peer
 }
 
 size_t BlockBytes(int64_t cap, int world) {
-  return static_cast<size_t>(2 + 4 * world) * cap * sizeof(float) + 2 * (kTpMaxWorld + 2) * sizeof(uint32_t);
+  return static_cast<size_t>(2 + 4 * world + 2) * cap * sizeof(float) + 2 * (kTpMaxWorld + 2) * sizeof(uint32_t);
 }
 uint2* PushedOf(void* block, int64_t cap) { return reinterpret_cast<uint2*>(static_cast<float*>(block) + 2 * cap); }
+uint2* BcastOf(void* block, int64_t cap, int world) {
+  return reinterpret_cast<uint2*>(static_cast<float*>(block) + static_cast<size_t>(2 + 4 * world) * cap);
+}
 uint32_t* FlagsOf(void* block, int64_t cap, int world) {
-  return reinterpret_cast<uint32_t*>(static_cast<float*>(block) + static_cast<size_t>(2 + 4 * world) * cap);
+  return reinterpret_cast<uint32_t*>(static_cast<float*>(block) + static_cast<size_t>(2 + 4 * world + 2) * cap);
 }
 uint32_t* PushFlagsOf(void* block, int64_t cap, int world) { return FlagsOf(block, cap, world) + kTpMaxWorld + 2; }
 
@@ -234,6 +237,7 @@ bool TpPushLink(b200_tp* tp, QmmTp* out) {
   out->count = pf + kTpMaxWorld;
   out->done = pf + kTpMaxWorld + 1;
   out->src = PushedOf(tp->block, tp->cap);
+  out->bcast = BcastOf(tp->block, tp->cap, tp->world);
   for (int r = 0; r < tp->world; ++r) {
     out->dst[r] = PushedOf(tp->peer_block[r], tp->cap) + static_cast<int64_t>(tp->rank) * tp->cap;
   }

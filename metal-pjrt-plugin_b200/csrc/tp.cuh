@@ -9,6 +9,8 @@ constexpr int kTpMaxWorld = 8;
 //   uint2 pushed[2][world][cap]    two alternating slots of EVERY rank's partial sums, stored here by
 //                                  the projections of those ranks (rank r writes sub-slot r) as 8-byte
 //                                  lines {f32 bits, number of the push exchange the value belongs to}
+//   uint2 bcast[2][cap / 2]        two alternating slots of this rank's OWN summed rows, published by the CTAs of
+//                                  the consuming projection for one another: lines {two bf16, exchange number}
 //   uint32 flags[kTpMaxWorld]      flags[r]: last pull exchange for which rank r's partial is ready
 //                                  (written by rank r over NVLink)
 //   uint32 seq                     pull exchanges this rank has completed
@@ -43,6 +45,7 @@ struct QmmTp {
   uint2* dst[kTpMaxWorld] = {};           // this rank's sub-slot (of slot 0) on every rank
   uint32_t* done = nullptr;
   const uint2* src = nullptr;             // slot 0 of pushed[][][] in this rank's memory
+  uint2* bcast = nullptr;                 // slot 0 of bcast[][] in this rank's memory
   void* x_out = nullptr;
 };
 b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_params* p, const QmmTp* tp);
