@@ -170,13 +170,13 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   // after them sums the ranks' sub-slots from its own memory, adds the residual and
   // applies the RMSNorm while it stages its input: no kernel of its own for the exchange.
   QmmTp link;
-  // (Up to 2 rows by default: every CTA of the consuming projection sums all ranks' rows for
-  // itself, which at 8 rows costs more than the one exchange kernel it replaces - measured on
-  // 2 GPUs: 2.53 against 2.63 ms per step at batch 1, 4.9 against 3.8 ms at batch 8.
+  // (Up to 4 rows by default.  Measured on 2 GPUs, ms per step, push against the separate exchange kernel:
+  // batch 1 2.03 against 2.63, batch 4 2.81 against 2.84, batch 8 3.89 against 3.50: the staging of the
+  // consuming projection re-reads the whole summed row in every CTA, which grows with the rows.
   // B200_TP_PUSH_ROWS overrides the limit, B200_TP_PULL=1 switches the push off.)
   static const int push_rows = [] {
     const char* v = std::getenv("B200_TP_PUSH_ROWS");
-    return v != nullptr ? std::atoi(v) : 2;
+    return v != nullptr ? std::atoi(v) : 4;
   }();
   const bool push = peer && batch <= std::min(push_rows, 8) && !EnvFlag("B200_TP_PULL") && TpPushLink(d->tp, &link);
   // Up to 8 rows the RMSNorm in front of a projection is fused into its input
