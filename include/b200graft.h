@@ -429,7 +429,14 @@ b200_status b200_tp_all_gather_f32(b200_tp* tp, b200_stream stream, const void* 
  * its f32 partial sums; consecutive exchanges must alternate slots 0, 1, 0, ...
  * b200_tp_sum_residual_norm: x[batch, hidden] (bf16) += bf16(sum over ranks of the slot),
  * h = rms_norm(x) * gain; peers are awaited with a bounded spin (B200_TIMEOUT through the
- * context's status word). */
+ * context's status word; after a wait that ran out no peer memory is read).
+ * A decoder created with a connected group goes one step further for up to 4 rows per step
+ * (B200_TP_PUSH_ROWS, at most 8; B200_TP_PULL=1 switches it off): its o / down projections
+ * store each f32 partial sum together with the exchange number as one 8-byte line into
+ * every rank's block (max_floats a multiple of 8), and the projection that follows forms
+ * the sum from its own memory while it stages its input (no exchange kernel, no flags or
+ * fences; bounded re-reads, wait ids 400 + rank and 450).  No TMA, multicast or multimem
+ * touches peer memory anywhere in this library: plain loads and stores only. */
 #define B200_TP_PEER_HANDLE_BYTES 64
 b200_status b200_tp_peer_alloc(b200_tp* tp, int64_t max_floats, void* handle_out /* B200_TP_PEER_HANDLE_BYTES */);
 b200_status b200_tp_peer_connect(b200_tp* tp, const void* handles /* world x B200_TP_PEER_HANDLE_BYTES */);
