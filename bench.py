@@ -383,6 +383,10 @@ def run_ours(args):
         cfg_local = parallel.local_config(CFG, world)
         if args.collective == "peer":   # sums over ranks as one kernel over peer memory
             tp.connect_peers(args.batch * CFG["hidden"])
+    elif args.self_exchange:   # one GPU through the sharded code path (a group of one rank): a diagnostic, not the default
+        from metal_pjrt_plugin_b200 import parallel
+        tp = parallel.TensorParallel.single(ctx)
+        tp.connect_peers(args.batch * CFG["hidden"])
     B = args.batch
     params, cache = build_device_model(pkg, cfg_local, B, device, 4, world, rank, ctx)
     dec = pkg.qwen3.Decoder(params, cache, cfg_local, max_batch=B, ctx=ctx, tp=tp)
@@ -494,6 +498,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the stand-alone operator timings")
+    ap.add_argument("--self-exchange", action="store_true",
+                    help="1 GPU only: run the step through the tensor-parallel code path with a group of one rank "
+                         "(what the exchange machinery costs without any NVLink traffic)")
     ap.add_argument("--quick-ops", action="store_true", help="fewer shapes and repetitions in the stand-alone operator timings")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the sums over ranks by the library's peer-memory kernel, or by ncclAllReduce")

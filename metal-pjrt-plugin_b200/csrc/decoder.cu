@@ -162,7 +162,9 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   b200_context* ctx = d->ctx;
   const int64_t E = c.hidden, HD = static_cast<int64_t>(c.heads) * c.head_dim;
   const int64_t QKV = static_cast<int64_t>(c.heads + 2 * c.kv_heads) * c.head_dim;
-  const bool tp = d->tp != nullptr && d->tp->world > 1;
+  // (A group of ONE rank takes the sharded path too: the whole exchange, lines and two-level sum
+  // included, then runs on a single GPU, which is how a one-GPU test or profile reaches that code.)
+  const bool tp = d->tp != nullptr;
   const bool peer = tp && d->tp->peer && static_cast<int64_t>(batch) * E <= d->tp->cap;
 
   // Push exchange (up to 8 rows, peers connected): the o / down projections store their f32
@@ -362,7 +364,7 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
   if (e == cudaSuccess)
     e = cudaMalloc(reinterpret_cast<void**>(&d->attn_scratch),
                    b200_attention_scratch_bytes(c.max_batch, c.heads, c.head_dim, c.max_len));
-  if (e == cudaSuccess && tp != nullptr && tp->world > 1) e = Alloc(&d->logits_local, B * c.vocab);
+  if (e == cudaSuccess && tp != nullptr) e = Alloc(&d->logits_local, B * c.vocab);
   if (e == cudaSuccess && c.max_batch > 8) e = Alloc(&d->logits_bf16, B * c.vocab);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->capture_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = Alloc(&d->inv_freq, static_cast<size_t>(c.head_dim / 2));

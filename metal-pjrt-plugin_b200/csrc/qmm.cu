@@ -103,11 +103,11 @@ struct QmmArgs {
   uint32_t* tp_done;                     // CTAs of the pushing kernel that have finished
   const uint2* tp_src;                   // prologue: slot 0 of the lines in this rank's memory, [world][cap]
   long long tp_cap;                      // floats per sub-slot; a slot is world sub-slots
-  int tp_nowait;                         // measurement only, wrong results: B200_TP_NOWAIT=1 take the lines as they are (no waiting),
-                                         // =2 do not read them at all, =4 (pusher) store to this rank's own memory only
+  int tp_nowait;                         // measurement only, wrong results: bits of B200_TP_NOWAIT: 1 take the lines as they are (no
+                                         // waiting), 2 do not read the ranks' lines at all, 4 (pusher) store to this rank's own memory
+                                         // only, 8 (pusher) no exchange count at the end, 16 (pusher) plain instead of volatile stores
   __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
-  uint2* tp_bcast;                       // two-level sum: slot 0 of this rank's lines {two bf16 of the new residual, exchange number};
-                                         // null: every CTA sums the ranks' lines itself
+  uint2* tp_bcast;                       // slot 0 of this rank's lines {two bf16 of the new residual row, exchange number}
 };
 
 constexpr int kEpilogueGemm = 100;
@@ -124,50 +124,97 @@ __device__ __forceinline__ uint4 ld_lines2(const uint2* p) {
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
+// The slow path of every wait on lines, out of line (the kernels are sensitive to their code size):
+// spins, bounded, until the `quads` 16-byte pairs of lines at p (and at p + pitch, ... for `ranks`
+// sub-slots) all carry exchange n.  Once any wait of this context has run out (the status word is
+// set) nobody waits again.
+__device__ __noinline__ void tp_wait_lines(const uint2* p, size_t pitch, int ranks, int quads, uint32_t n, int* status, int where) {
+  const long long t0 = clock64();
+  for (;;) {
+    int late = -1;
+    for (int r = ranks - 1; r >= 0; --r)
+      for (int j = 0; j < quads; ++j) {
+        const uint4 v = ld_lines2(p + r * pitch + 2 * j);
+        if (v.y != n || v.w != n) late = r;
+      }
+    if (late < 0) return;
+    if (*reinterpret_cast<volatile int*>(status) != 0) return;
+    if (clock64() - t0 > 4000000000ll) {
+      report_timeout(status, where + late);   // the first rank whose lines are missing
+      return;
+    }
+  }
+}
+
 // Eight consecutive lines of exchange n from each of R ranks' sub-slots (p 16-byte aligned, `pitch`
 // lines between sub-slots), added to sum[] in rank order.  All R x 4 loads are in flight together
-// (one trip to L2 for R ranks).  Waits, bounded, for lines that have not landed yet; once any wait
-// of this context has run out (the status word is set) nobody waits again and the missing values
-// count as zero.
+// (one trip to L2 for R ranks); lines that have not landed yet are waited for out of line, and
+// count as zero if that wait gives up.
 template <int R>
 __device__ __forceinline__ void add_lines8(const uint2* p, size_t pitch, uint32_t n, int* status, int where, float (&sum)[8],
                                            bool nowait) {
   uint4 v[R][4];
-  long long t0 = 0;
-  bool ok;
-  for (;;) {
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[r][j] = ld_lines2(p + r * pitch + 2 * j);
+  bool ok = true;
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ok = ok && v[r][j].y == n && v[r][j].w == n;
+  if (!ok && !nowait) {
+    tp_wait_lines(p, pitch, R, 4, n, status, where);
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int j = 0; j < 4; ++j) v[r][j] = ld_lines2(p + r * pitch + 2 * j);
-    ok = true;
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) ok = ok && v[r][j].y == n && v[r][j].w == n;
-    if (ok || nowait) break;
-    if (*reinterpret_cast<volatile int*>(status) != 0) break;
-    if (t0 == 0) {
-      t0 = clock64();
-    } else if (clock64() - t0 > 4000000000ll) {
-      int late = 0;   // the first rank whose lines are missing
-#pragma unroll
-      for (int r = R - 1; r >= 0; --r)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (v[r][j].y != n || v[r][j].w != n) late = r;
-      report_timeout(status, where + late);
-      break;
-    }
   }
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const bool have = v[r][j].y == n && v[r][j].w == n;
+      const bool have = (v[r][j].y == n && v[r][j].w == n) || nowait;
       sum[2 * j] += have ? __uint_as_float(v[r][j].x) : 0.0f;
       sum[2 * j + 1] += have ? __uint_as_float(v[r][j].z) : 0.0f;
     }
+}
+
+// One partial sum into sub-slot `rank` of every rank's block (out of line: seven call sites).
+__device__ __noinline__ void tp_push_value(uint2* const* dst, int world, int rank, int mode, size_t idx, float v, uint32_t n) {
+  for (int r = 0; r < world; ++r) {
+    if ((mode & 4) && r != rank) continue;
+    if (mode & 16) dst[r][idx] = make_uint2(__float_as_uint(v), n);
+    else st_line(dst[r] + idx, v, n);
+  }
+}
+
+// The first level of the sum over ranks, by the CTAs of the consuming projection together: the rows
+// are cut into runs of 8 values dealt out over the CTAs (8 consecutive runs per CTA and step, so a
+// quarter warp reads 512 contiguous bytes per rank); the owner of a run adds the ranks' lines in
+// rank order (identical sums on every rank) and the old residual, writes the new residual row, and
+// publishes the 8 bf16 values as four {two values, exchange number} lines in this rank's memory.
+__device__ __noinline__ void tp_reduce_publish(const uint2* slot, size_t pitch, int world, uint32_t n, int* status, int mode,
+                                               const __nv_bfloat16* x, int ldx, int M, int K, __nv_bfloat16* x_out, uint2* bc,
+                                               int cta_id, int n_ctas, int tid, int threads) {
+  const int runs = M * (K / 8);
+  for (int run = cta_id * 8 + (tid & 7) + (tid >> 3) * n_ctas * 8; run < runs; run += (threads / 8) * n_ctas * 8) {
+    const int m = run / (K / 8), k = (run % (K / 8)) * 8;
+    float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const uint2* base = slot + static_cast<size_t>(m) * K + k;
+    int r = (mode & 2) ? world : 0;
+    for (; r + 2 <= world; r += 2) add_lines8<2>(base + r * pitch, pitch, n, status, 400 + r, sum, (mode & 1) != 0);
+    if (r < world) add_lines8<1>(base + r * pitch, pitch, n, status, 400 + r, sum, (mode & 1) != 0);
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * ldx + k));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_bf16(bf16_lo(w[j]) + bf16_round(sum[2 * j]), bf16_hi(w[j]) + bf16_round(sum[2 * j + 1]));
+    if (x_out != nullptr) *reinterpret_cast<uint4*>(x_out + static_cast<size_t>(m) * K + k) = make_uint4(o[0], o[1], o[2], o[3]);
+    uint2* dst = bc + (static_cast<size_t>(m) * K + k) / 2;
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o[0]), "r"(n), "r"(o[1]), "r"(n) : "memory");
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(o[2]), "r"(n), "r"(o[3]), "r"(n) : "memory");
+  }
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -291,10 +338,7 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
   if (TP && a.epilogue == kEpiloguePush) {
     // one line per value into every rank's memory (its own included); the slot alternates with the exchange number
     const uint32_t n_x = *a.tp_count + 1u;
-    const size_t so_ = static_cast<size_t>(n_x & 1u) * a.tp_world * a.tp_cap + o;
-#pragma unroll
-    for (int r = 0; r < kTpMaxWorld; ++r)
-      if (r < a.tp_world && (a.tp_nowait != 4 || r == a.tp_rank)) st_line(a.tp_dst[r] + so_, v, n_x);
+    tp_push_value(a.tp_dst, a.tp_world, a.tp_rank, a.tp_nowait, static_cast<size_t>(n_x & 1u) * a.tp_world * a.tp_cap + o, v, n_x);
     return;
   }
   if (a.epilogue == B200_QMM_OUT_F32_RAW) {
@@ -326,7 +370,7 @@ __device__ __forceinline__ void store_output(const QmmArgs& a, float v, int m, i
 // TP: the build that takes part in the tensor-parallel exchange (sums the ranks' partial sums while it
 // stages x, or pushes its own from the epilogue); the others carry none of that code.
 template <int FMT, int MB, int RT, bool GROUPED, int KG, bool LEAN = (KG > 0), bool VEC = LEAN, bool TP = false>
-__global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constant__ QmmArgs a) {
   static_assert(KG == 0 || LEAN, "the unrolled variants are lean");
   static_assert(!LEAN || VEC, "lean implies 16-byte loads");
   using F = Fmt<FMT>;
@@ -481,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     // Tensor parallel: x is the old residual; the new one is x + bf16(sum over ranks of the partial
     // sums that the K-sharded projection before this one pushed into every rank's memory as
     // {value, exchange number} lines).  That kernel has finished on this rank (the wait above), so
-    // the exchange number is final; a peer's line that has not landed yet is read again (bounded).
+    // the exchange number is final; a peer's line that has not landed yet is waited for (bounded).
     // Only this rank's own memory is ever read.
     const uint2* tp_slot = nullptr;
     const uint2* tp_bc = nullptr;
@@ -489,85 +533,36 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
     if (TP && a.tp_src != nullptr) {
       tp_n = *a.tp_count;
       tp_slot = a.tp_src + static_cast<size_t>(tp_n & 1u) * a.tp_world * a.tp_cap;
-      if (a.tp_bcast != nullptr) {
-        // Two levels: the sum over ranks is formed ONCE per rank.  The row is cut into
-        // runs of 8 values that are dealt out over the CTAs of this kernel; the owner of a run adds the
-        // ranks' lines and the old residual, writes the new residual row, and publishes the 8 bf16 values
-        // as four {two values, exchange number} lines in this rank's own memory, where every CTA then
-        // reads the whole new row (K / 2 lines instead of world * K).  All CTAs of the grid are resident
-        // (one per SM), so waiting for a line another CTA of the grid publishes cannot deadlock; the wait
-        // is bounded like every other.
-        uint2* bc = a.tp_bcast + static_cast<size_t>(tp_n & 1u) * (a.tp_cap / 2);
-        tp_bc = bc;
-        const int n_ctas = static_cast<int>(gridDim.x * gridDim.y), cta_id = static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x);
-        const int runs = a.M * (a.K / 8);
-        const size_t pitch = static_cast<size_t>(a.tp_cap);
-        for (int run = cta_id * 8 + (tid & 7) + (tid >> 3) * n_ctas * 8; run < runs; run += (kConsumerThreads / 8) * n_ctas * 8) {
-          // (8 consecutive runs = 64 values per CTA and step, so a warp's quarter reads 512 contiguous bytes per rank)
-          const int m = run / (a.K / 8), k = (run % (a.K / 8)) * 8;
-          float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-          const uint2* base = tp_slot + static_cast<size_t>(m) * a.K + k;
-          int r = a.tp_nowait == 2 ? a.tp_world : 0;
-#pragma unroll 1
-          for (; r + 2 <= a.tp_world; r += 2) add_lines8<2>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
-          if (r < a.tp_world) add_lines8<1>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
-          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(m) * a.ldx + k));
-          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-          uint32_t o[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            o[j] = pack_bf16(bf16_lo(w[j]) + bf16_round(sum[2 * j]), bf16_hi(w[j]) + bf16_round(sum[2 * j + 1]));
-          if (a.x_out != nullptr) *reinterpret_cast<uint4*>(a.x_out + static_cast<size_t>(m) * a.K + k) = make_uint4(o[0], o[1], o[2], o[3]);
-          uint2* dst = bc + (static_cast<size_t>(m) * a.K + k) / 2;
-          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o[0]), "r"(tp_n), "r"(o[1]), "r"(tp_n) : "memory");
-          asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(o[2]), "r"(tp_n), "r"(o[3]), "r"(tp_n) : "memory");
-        }
-      }
+      // Two levels: the sum over ranks is formed ONCE per rank, by the CTAs of this kernel together
+      // (tp_reduce_publish), and every CTA then reads the whole new row as this rank published it
+      // (K / 2 lines instead of world * K).  All CTAs of the grid are resident (one per SM), so waiting
+      // for a line another CTA of the grid publishes cannot deadlock; the wait is bounded like every other.
+      tp_bc = a.tp_bcast + static_cast<size_t>(tp_n & 1u) * (a.tp_cap / 2);
+      tp_reduce_publish(tp_slot, static_cast<size_t>(a.tp_cap), a.tp_world, tp_n, a.status, a.tp_nowait, a.x, a.ldx, a.M, a.K,
+                        a.x_out, a.tp_bcast + static_cast<size_t>(tp_n & 1u) * (a.tp_cap / 2),
+                        static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x), static_cast<int>(gridDim.x * gridDim.y), tid,
+                        kConsumerThreads);
     }
-    // eight values of row m starting at k, the partial sums folded in
+    // eight values of row m starting at k: of x, or of the new residual row as this rank published it
     auto load_x8 = [&](int m, int k, float* dst) {
-      if (TP && tp_bc != nullptr) {   // the new residual row as this rank published it
+      uint32_t w[4];
+      if (TP && tp_bc != nullptr) {
         const uint2* src = tp_bc + (static_cast<size_t>(m) * a.K + k) / 2;
-        uint4 v0, v1;
-        long long t0 = 0;
-        for (;;) {
+        uint4 v0 = ld_lines2(src), v1 = ld_lines2(src + 2);
+        if (!(v0.y == tp_n && v0.w == tp_n && v1.y == tp_n && v1.w == tp_n) && !(a.tp_nowait & 1)) {
+          tp_wait_lines(src, 0, 1, 2, tp_n, a.status, 450);
           v0 = ld_lines2(src);
           v1 = ld_lines2(src + 2);
-          if ((v0.y == tp_n && v0.w == tp_n && v1.y == tp_n && v1.w == tp_n) || a.tp_nowait != 0) break;
-          if (*reinterpret_cast<volatile int*>(a.status) != 0) break;
-          if (t0 == 0) {
-            t0 = clock64();
-          } else if (clock64() - t0 > 4000000000ll) {
-            report_timeout(a.status, 450);
-            break;
-          }
         }
-        const uint32_t w[4] = {v0.x, v0.z, v1.x, v1.z};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          dst[2 * j] = bf16_lo(w[j]);
-          dst[2 * j + 1] = bf16_hi(w[j]);
-        }
-        return;
+        w[0] = v0.x; w[1] = v0.z; w[2] = v1.x; w[3] = v1.z;
+      } else {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(m) * a.ldx + k));
+        w[0] = raw.x; w[1] = raw.y; w[2] = raw.z; w[3] = raw.w;
       }
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(m) * a.ldx + k));
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         dst[2 * j] = bf16_lo(w[j]);
         dst[2 * j + 1] = bf16_hi(w[j]);
-      }
-      if (TP && tp_slot != nullptr) {
-        float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        const uint2* base = tp_slot + static_cast<size_t>(m) * a.K + k;
-        // rank order on every rank: identical sums everywhere; two ranks' lines per trip to L2
-        const size_t pitch = static_cast<size_t>(a.tp_cap);
-        int r = a.tp_nowait == 2 ? a.tp_world : 0;
-#pragma unroll 1
-        for (; r + 2 <= a.tp_world; r += 2) add_lines8<2>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
-        if (r < a.tp_world) add_lines8<1>(base + r * pitch, pitch, tp_n, a.status, 400 + r, sum, a.tp_nowait != 0);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dst[j] = bf16_round(dst[j] + bf16_round(sum[j]));
       }
     };
     // RMSNorm in one pass: when every thread stages at most one 16-input unit of a whole row
@@ -654,11 +649,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
         if (TP && valid && tp_slot != nullptr) {
           load_x8(um, kbase + run0, e);
           load_x8(um, kbase + run1, e + 8);
-          if (blockIdx.x == 0 && a.x_out != nullptr && tp_bc == nullptr) {   // the new residual row, once (each K slice by its CTA of tile 0)
-            __nv_bfloat16* xo = a.x_out + static_cast<size_t>(um) * a.K + kbase;
-            *reinterpret_cast<uint4*>(xo + run0) = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
-            *reinterpret_cast<uint4*>(xo + run1) = make_uint4(pack_bf16(e[8], e[9]), pack_bf16(e[10], e[11]), pack_bf16(e[12], e[13]), pack_bf16(e[14], e[15]));
-          }
           load_run(a.gain, kbase + run0, gn);
           load_run(a.gain, kbase + run1, gn + 8);
         } else if (valid) {
@@ -1066,7 +1056,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const QmmArgs a) {
       cluster_arrive(n_my);
       cluster_wait(n_my);
     }
-    if (TP && a.epilogue == kEpiloguePush) {
+    if (TP && a.epilogue == kEpiloguePush && !(a.tp_nowait & 8)) {
       // The last CTA of this rank to finish counts the exchange (every CTA read the old count
       // before it got here).  Nothing else closes it: each line says which exchange it is.
       consumer_barrier();
@@ -1466,7 +1456,9 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   for (int r = 0; r < kTpMaxWorld; ++r) {
     a.tp_dst[r] = nullptr;
   }
-  if (tp != nullptr && tp->world > 1) {
+  static const bool force_tp_build = std::getenv("B200_QMM_FORCE_TP_BUILD") != nullptr;   // measurement only
+  if (force_tp_build && tp == nullptr && pl.mb == 1 && (pl.fmt == kInt4Seq || pl.fmt == kBf16)) a.tp_world = 1;
+  if (tp != nullptr && tp->world >= 1) {
     if (tp->push && tp->src != nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: a projection either pushes partial sums or consumes them");
     if (p->M * p->N > tp->cap && tp->push) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: partial sums exceed the exchange block");
     if ((pl.fmt != kInt4Seq && pl.fmt != kBf16) || pl.mb != 1)
@@ -1490,8 +1482,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
       a.tp_src = tp->src;
       a.tp_nowait = TpMeasureMode();
       a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
-      static const int two_level = [] { const char* v = std::getenv("B200_TP_TWO_LEVEL"); return v != nullptr ? atoi(v) : -1; }();
-      if (tp->bcast != nullptr && two_level != 0) a.tp_bcast = tp->bcast;   // (B200_TP_TWO_LEVEL=0: every CTA sums the ranks' lines itself)
+      a.tp_bcast = tp->bcast;
     }
   }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);

@@ -33,19 +33,28 @@ class TensorParallel:
         dist.broadcast_object_list(box, src=0)
         return cls(rank, world, box[0], ctx)
 
+    @classmethod
+    def single(cls, ctx=None):
+        """A group of one rank, made without torch.distributed.  A decoder created with it takes the
+        sharded code path (push exchange, lines, two-level sum) on one GPU: for tests and profiles."""
+        return cls(0, 1, cls.make_id(), ctx)
+
     def connect_peers(self, max_floats):
         """Allocates this rank's peer-exchange block (two slots of max_floats f32),
         gathers every rank's CUDA IPC handle over torch.distributed, maps the
         peers' blocks and synchronises the ranks.  After this the decoder's
         sums over ranks run as one kernel over peer memory instead of NCCL."""
-        import torch.distributed as dist
         buf = (C.c_char * _lib.TP_PEER_HANDLE_BYTES)()
         _lib.check(_lib.lib().b200_tp_peer_alloc(self.handle, max_floats, buf))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(buf))
+        handles = [bytes(buf)]
+        if self.world > 1:
+            import torch.distributed as dist
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(buf))
         packed = (C.c_char * (_lib.TP_PEER_HANDLE_BYTES * self.world)).from_buffer_copy(b"".join(handles))
         _lib.check(_lib.lib().b200_tp_peer_connect(self.handle, packed))
-        dist.barrier()
+        if self.world > 1:
+            dist.barrier()
         self.peers_connected = True
 
     def peer_partial(self, slot, shape):

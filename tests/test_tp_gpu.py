@@ -54,9 +54,6 @@ def _worker_body(rank, world, port, out_q, peers, hidden, B):
     else:
         os.environ.pop("B200_TP_PULL", None)
         os.environ["B200_TP_PUSH_ROWS"] = "8"   # the push at every batch it supports (the default stops at 2 rows)
-        # "push": the sum over ranks formed once per rank and published to the other CTAs (the default);
-        # "push1": every CTA of the consuming projection sums the ranks' lines itself
-        os.environ["B200_TP_TWO_LEVEL"] = "0" if peers == "push1" else "1"
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch
@@ -105,8 +102,7 @@ def _worker_body(rank, world, port, out_q, peers, hidden, B):
 
 
 @pytest.mark.parametrize("peers,hidden,B", [(False, 256, 3), ("pull", 256, 3), ("push", 256, 3), ("push", 512, 1),
-                                            ("push", 512, 2), ("push", 256, 8), ("push1", 256, 3), ("push1", 512, 1),
-                                            ("push1", 256, 8)])
+                                            ("push", 512, 2), ("push", 256, 8), ("push", 256, 4)])
 def test_tp2_decoder_matches_oracle(peers, hidden, B):
     """Sums over ranks by NCCL, by the exchange kernel that pulls the peers' partial sums, and by
     the projections pushing theirs (the two RMSNorm staging variants of the consuming
@@ -117,7 +113,7 @@ def test_tp2_decoder_matches_oracle(peers, hidden, B):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000 + {False: 0, "pull": 7, "push": 13, "push1": 19}[peers] + hidden // 64 + B
+    port = 29500 + os.getpid() % 2000 + {False: 0, "pull": 7, "push": 13}[peers] + hidden // 64 + B
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peers, hidden, B)) for r in range(2)]
     for p_ in procs:
         p_.start()
