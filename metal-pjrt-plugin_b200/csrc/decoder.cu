@@ -186,9 +186,8 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
   const bool fuse_norm = batch <= 8 && (!tp || push);
   __nv_bfloat16* xb[2] = {d->x, d->x2};
   int xp = 0;   // which of the two holds the current residual rows (push exchange)
-  QmmTp from_peers = link, to_peers = link;
+  QmmTp from_peers = link, to_peers = link;   // the projection that reads the summed rows / the one that pushes and sums
   to_peers.push = true;
-  to_peers.src = nullptr;
   B200_TRY(b200_embed(ctx, stream, d->embed, tokens, d->x, batch, E,
                       static_cast<int64_t>(c.vocab) * (d->tp != nullptr ? d->tp->world : 1)));
   if (!fuse_norm)
@@ -199,23 +198,25 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
       if (li == 0) {
         B200_TRY(Qmm(d, stream, L.qkv, xb[xp], d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM,
                      L.attn_norm));
-      } else {   // the down projection of the layer before pushed its partial sums
-        from_peers.x_out = xb[xp ^ 1];
+      } else {   // the down projection of the layer before pushed its partial sums and published the new residual rows
         B200_TRY(Qmm(d, stream, L.qkv, xb[xp], d->qkv, batch, QKV, E, B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM,
                      L.attn_norm, &from_peers));
-        xp ^= 1;
       }
       B200_TRY(b200_attention_step(ctx, stream, d->qkv, L.q_norm, L.k_norm, d->inv_freq, L.k_cache, L.v_cache, d->attn,
                                    pos, d->attn_scratch, batch, c.heads, c.kv_heads, c.head_dim, c.max_len,
                                    c.rope_theta, c.rms_eps));
+      to_peers.x_old = xb[xp];
+      to_peers.x_out = xb[xp ^ 1];
       B200_TRY(Qmm(d, stream, L.o, d->attn, link.dst[link.rank], batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr,
                    B200_QMM_PRO_NONE, nullptr, &to_peers));
-      from_peers.x_out = xb[xp ^ 1];
+      xp ^= 1;
       B200_TRY(Qmm(d, stream, L.gate_up, xb[xp], d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
                    nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm, &from_peers));
-      xp ^= 1;
+      to_peers.x_old = xb[xp];
+      to_peers.x_out = xb[xp ^ 1];
       B200_TRY(Qmm(d, stream, L.down, d->gu, link.dst[link.rank], batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr,
                    B200_QMM_PRO_SILU_MUL, nullptr, &to_peers));
+      xp ^= 1;
       continue;
     }
     if (fuse_norm)
@@ -311,7 +312,6 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
     p.M = batch;
     p.N = c.vocab;
     p.K = E;
-    from_peers.x_out = nullptr;   // the last down projection's partial sums; nobody needs the residual rows afterwards
     B200_TRY(QmmRunEx(ctx, stream, &p, push ? &from_peers : nullptr));
   }
   if (tp) B200_TRY(TpAllGather(d->tp, stream, d->logits_local, logits, static_cast<int64_t>(batch) * c.vocab, B200_F32));

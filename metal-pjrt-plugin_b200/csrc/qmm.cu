@@ -101,12 +101,13 @@ struct QmmArgs {
   uint2* tp_dst[kTpMaxWorld];            // epilogue kEpiloguePush: slot 0 of this rank's sub-slot on every rank
   uint32_t* tp_count;                    // exchanges this rank has pushed (device memory)
   uint32_t* tp_done;                     // CTAs of the pushing kernel that have finished
-  const uint2* tp_src;                   // prologue: slot 0 of the lines in this rank's memory, [world][cap]
+  const uint2* tp_src;                   // pusher: slot 0 of the ranks' lines in this rank's memory, [world][cap]
   long long tp_cap;                      // floats per sub-slot; a slot is world sub-slots
   int tp_nowait;                         // measurement only, wrong results: bits of B200_TP_NOWAIT: 1 take the lines as they are (no
                                          // waiting), 2 do not read the ranks' lines at all, 4 (pusher) store to this rank's own memory
                                          // only, 8 (pusher) no exchange count at the end, 16 (pusher) plain instead of volatile stores
-  __nv_bfloat16* x_out;                  // prologue with tp_src: the new residual rows (written by the CTAs of tile 0)
+  __nv_bfloat16* x_out;                  // pusher: where the new residual rows go
+  const __nv_bfloat16* tp_x_old;         // pusher: the residual rows the sum over ranks is added to, [M, N]
   uint2* tp_bcast;                       // slot 0 of this rank's lines {two bf16 of the new residual row, exchange number}
 };
 
@@ -522,26 +523,16 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     scale_load(static_cast<int>(blockIdx.x) * R);
     scale_store(static_cast<int>(blockIdx.x) * R, so);
     pdl_wait();  // x (and the residual) come from the previous kernel
-    // Tensor parallel: x is the old residual; the new one is x + bf16(sum over ranks of the partial
-    // sums that the K-sharded projection before this one pushed into every rank's memory as
-    // {value, exchange number} lines).  That kernel has finished on this rank (the wait above), so
-    // the exchange number is final; a peer's line that has not landed yet is waited for (bounded).
-    // Only this rank's own memory is ever read.
-    const uint2* tp_slot = nullptr;
+    // Tensor parallel: x is the new residual row, bf16(old + bf16(sum over ranks of the partial sums of
+    // the K-sharded projection before this one)), which the CTAs of that projection formed at their
+    // end and published as {two values, exchange number} lines in this rank's memory.  That kernel
+    // has finished on this rank (the wait above), so the exchange number is final and the lines are
+    // there; the bounded wait behind the first read only ever runs in the measurement modes.
     const uint2* tp_bc = nullptr;
     uint32_t tp_n = 0;
-    if (TP && a.tp_src != nullptr) {
+    if (TP && a.tp_bcast != nullptr && a.epilogue != kEpiloguePush) {
       tp_n = *a.tp_count;
-      tp_slot = a.tp_src + static_cast<size_t>(tp_n & 1u) * a.tp_world * a.tp_cap;
-      // Two levels: the sum over ranks is formed ONCE per rank, by the CTAs of this kernel together
-      // (tp_reduce_publish), and every CTA then reads the whole new row as this rank published it
-      // (K / 2 lines instead of world * K).  All CTAs of the grid are resident (one per SM), so waiting
-      // for a line another CTA of the grid publishes cannot deadlock; the wait is bounded like every other.
       tp_bc = a.tp_bcast + static_cast<size_t>(tp_n & 1u) * (a.tp_cap / 2);
-      tp_reduce_publish(tp_slot, static_cast<size_t>(a.tp_cap), a.tp_world, tp_n, a.status, a.tp_nowait, a.x, a.ldx, a.M, a.K,
-                        a.x_out, a.tp_bcast + static_cast<size_t>(tp_n & 1u) * (a.tp_cap / 2),
-                        static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x), static_cast<int>(gridDim.x * gridDim.y), tid,
-                        kConsumerThreads);
     }
     // eight values of row m starting at k: of x, or of the new residual row as this rank published it
     auto load_x8 = [&](int m, int k, float* dst) {
@@ -579,7 +570,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         ss[m] = 0.0f;
         if (m < a.M) {
           const __nv_bfloat16* xr = a.x + static_cast<size_t>(m) * a.ldx;
-          if (TP && x_vec && tp_slot != nullptr) {
+          if (TP && x_vec && tp_bc != nullptr) {
             for (int i = tid * 8; i < a.K; i += kConsumerThreads * 8) {
               float e8[8];
               load_x8(m, i, e8);
@@ -646,7 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             }
           };
         const __nv_bfloat16* xr = a.x + static_cast<size_t>(valid ? um : 0) * a.ldx;
-        if (TP && valid && tp_slot != nullptr) {
+        if (TP && valid && tp_bc != nullptr) {
           load_x8(um, kbase + run0, e);
           load_x8(um, kbase + run1, e + 8);
           load_run(a.gain, kbase + run0, gn);
@@ -1056,12 +1047,24 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
       cluster_arrive(n_my);
       cluster_wait(n_my);
     }
-    if (TP && a.epilogue == kEpiloguePush && !(a.tp_nowait & 8)) {
-      // The last CTA of this rank to finish counts the exchange (every CTA read the old count
-      // before it got here).  Nothing else closes it: each line says which exchange it is.
+    if (TP && a.epilogue == kEpiloguePush) {
+      // This CTA's lines are on their way.  Now the sum over ranks, formed ONCE per rank by the CTAs of
+      // this kernel together (tp_reduce_publish): CTAs that finish their tiles early do it while the
+      // others still stream weights, and the projection that follows finds the new residual row
+      // published in this rank's memory (K / 2 lines instead of world * K to read).  All CTAs of the
+      // grid are resident (one per SM), so waiting for lines that other CTAs of the grid, or the
+      // peers, still have to store cannot deadlock; the wait is bounded like every other.
       consumer_barrier();
-      if (tid == 0) {
-        const uint32_t n = *a.tp_count + 1u;
+      const uint32_t n = *a.tp_count + 1u;
+      if (a.tp_bcast != nullptr)
+        tp_reduce_publish(a.tp_src + static_cast<size_t>(n & 1u) * a.tp_world * a.tp_cap, static_cast<size_t>(a.tp_cap), a.tp_world, n,
+                          a.status, a.tp_nowait, a.tp_x_old, a.N, a.M, a.N, a.x_out,
+                          a.tp_bcast + static_cast<size_t>(n & 1u) * (a.tp_cap / 2),
+                          static_cast<int>(blockIdx.y * gridDim.x + blockIdx.x), static_cast<int>(gridDim.x * gridDim.y), tid,
+                          kConsumerThreads);
+      // The last CTA of this rank to finish counts the exchange (every CTA read the old count before).
+      consumer_barrier();
+      if (tid == 0 && !(a.tp_nowait & 8)) {
         __threadfence();
         if (atomicAdd(a.tp_done, 1u) == gridDim.x * gridDim.y - 1u) {
           *a.tp_done = 0u;
@@ -1452,6 +1455,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   a.tp_cap = 0;
   a.tp_nowait = 0;
   a.x_out = nullptr;
+  a.tp_x_old = nullptr;
   a.tp_bcast = nullptr;
   for (int r = 0; r < kTpMaxWorld; ++r) {
     a.tp_dst[r] = nullptr;
@@ -1459,30 +1463,30 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   static const bool force_tp_build = std::getenv("B200_QMM_FORCE_TP_BUILD") != nullptr;   // measurement only
   if (force_tp_build && tp == nullptr && pl.mb == 1 && (pl.fmt == kInt4Seq || pl.fmt == kBf16)) a.tp_world = 1;
   if (tp != nullptr && tp->world >= 1) {
-    if (tp->push && tp->src != nullptr) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: a projection either pushes partial sums or consumes them");
     if (p->M * p->N > tp->cap && tp->push) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: partial sums exceed the exchange block");
     if ((pl.fmt != kInt4Seq && pl.fmt != kBf16) || pl.mb != 1)
       return Fail(B200_UNIMPLEMENTED, "b200_qmm: the exchange takes sequential int4 or bf16 weights and up to 8 rows");
+    if (tp->src == nullptr || tp->bcast == nullptr || tp->count == nullptr)
+      return Fail(B200_INVALID_ARGUMENT, "b200_qmm: the exchange is not connected");
     a.tp_world = tp->world;
     a.tp_rank = tp->rank;
     a.tp_cap = tp->cap;
     a.tp_count = tp->count;
+    a.tp_bcast = tp->bcast;
+    a.tp_nowait = TpMeasureMode();
     if (tp->push) {
-      if (p->epilogue != B200_QMM_OUT_F32_RAW || a.ldo != a.N)
-        return Fail(B200_INVALID_ARGUMENT, "b200_qmm: pushed partial sums are dense raw f32");
+      if (p->epilogue != B200_QMM_OUT_F32_RAW || a.ldo != a.N || a.N % 8 != 0 || tp->x_old == nullptr || tp->x_out == nullptr ||
+          !Aligned(tp->x_old, 16) || !Aligned(tp->x_out, 16))
+        return Fail(B200_INVALID_ARGUMENT, "b200_qmm: pushed partial sums are dense raw f32 rows of a multiple of 8 values, with the residual rows they are added to");
       a.epilogue = kEpiloguePush;
       a.tp_done = tp->done;
-      a.tp_nowait = TpMeasureMode();
-      for (int r = 0; r < tp->world; ++r) {
-        a.tp_dst[r] = tp->dst[r];
-      }
-    } else if (tp->src != nullptr) {
-      if (p->prologue != B200_QMM_PRO_RMSNORM || !a.x_vec || a.ldx != a.K || a.K % 8 != 0 || p->M * p->K > tp->cap)
-        return Fail(B200_INVALID_ARGUMENT, "b200_qmm: summing the ranks' partial sums goes with the RMSNorm prologue on dense, aligned rows");
       a.tp_src = tp->src;
-      a.tp_nowait = TpMeasureMode();
+      a.tp_x_old = static_cast<const __nv_bfloat16*>(tp->x_old);
       a.x_out = static_cast<__nv_bfloat16*>(tp->x_out);
-      a.tp_bcast = tp->bcast;
+      for (int r = 0; r < tp->world; ++r) a.tp_dst[r] = tp->dst[r];
+    } else {
+      if (p->prologue != B200_QMM_PRO_RMSNORM || !a.x_vec || a.ldx != a.K || a.K % 8 != 0 || p->M * p->K > tp->cap)
+        return Fail(B200_INVALID_ARGUMENT, "b200_qmm: reading the summed rows goes with the RMSNorm prologue on dense, aligned rows");
     }
   }
   const dim3 grid(static_cast<unsigned>(pl.grid_x), pl.split, 1);

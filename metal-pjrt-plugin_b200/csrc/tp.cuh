@@ -32,10 +32,12 @@ namespace b200 {
 // How one projection (b200_qmm) takes part in the push exchange of a K-sharded product's
 // partial sums.  push: its epilogue stores each raw f32 partial sum, together with the number
 // of the exchange, as one 8-byte line into sub-slot `rank` of every rank's block (plain
-// stores over NVLink; no flag, no fence: the line itself says when it is there).  src: its
-// RMSNorm prologue reads x as bf16(x + bf16(sum over ranks, in rank order, of the sub-slots in
-// THIS rank's memory)), reading a line again (bounded) until it carries the expected exchange
-// number; the CTAs of its first row tile write those new residual rows to x_out.  Slots
+// stores over NVLink; no flag, no fence: the line itself says when it is there).  At their
+// end the CTAs of the same kernel form the sum over ranks once per rank: each owns some runs
+// of 8 values, adds the ranks' lines from THIS rank's memory in rank order (waiting, bounded,
+// for lines that have not landed) and the old residual x_old, writes the new residual rows to
+// x_out and publishes them as {two bf16, exchange number} lines.  Not push: the projection
+// that follows reads those published rows as the input of its RMSNorm prologue.  Slots
 // alternate with the exchange number, which lives in device memory (a captured graph replays).
 struct QmmTp {
   int world = 0, rank = 0;
@@ -46,7 +48,8 @@ struct QmmTp {
   uint32_t* done = nullptr;
   const uint2* src = nullptr;             // slot 0 of pushed[][][] in this rank's memory
   uint2* bcast = nullptr;                 // slot 0 of bcast[][] in this rank's memory
-  void* x_out = nullptr;
+  const void* x_old = nullptr;            // push: residual rows [M, N] the sum is added to
+  void* x_out = nullptr;                  // push: where the new residual rows go
 };
 b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_params* p, const QmmTp* tp);
 // Fills the fields above (push and consume sides) from a connected group; false when the exchange is not connected.
