@@ -433,9 +433,10 @@ b200_status b200_tp_all_gather_f32(b200_tp* tp, b200_stream stream, const void* 
  * A decoder created with a connected group goes one step further for up to 4 rows per step
  * (B200_TP_PUSH_ROWS, at most 8; B200_TP_PULL=1 switches it off): its o / down projections
  * store each f32 partial sum together with the exchange number as one 8-byte line into
- * every rank's block (max_floats a multiple of 8), and the projection that follows forms
- * the sum from its own memory while it stages its input (no exchange kernel, no flags or
- * fences; bounded re-reads, wait ids 400 + rank and 450).  No TMA, multicast or multimem
+ * every rank's block (max_floats a multiple of 8); at their end the CTAs of the same kernel
+ * form the sum over ranks once, from this rank's own memory, and publish the new residual
+ * rows there for the projection that follows (no exchange kernel, no flags or fences;
+ * bounded waits, ids 400 + rank and 450).  No TMA, multicast or multimem
  * touches peer memory anywhere in this library: plain loads and stores only. */
 #define B200_TP_PEER_HANDLE_BYTES 64
 b200_status b200_tp_peer_alloc(b200_tp* tp, int64_t max_floats, void* handle_out /* B200_TP_PEER_HANDLE_BYTES */);
