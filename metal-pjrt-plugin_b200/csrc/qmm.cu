@@ -14,14 +14,19 @@
 //   * the weight copies do not depend on the previous kernel, so they are
 //     issued BEFORE griddepcontrol.wait: under programmatic dependent launch
 //     the next product's weights stream while the previous kernel drains;
-//   * eight consumer warps take one 64-input group each per 512-input chunk:
-//     nibbles / bytes are widened to bf16 in registers (one lop3 per two
-//     nibbles, 128 + q with the 128 folded into the offset term) and fed to
-//     mma.sync m16n8k16 with the batch as the 8-wide operand; the inputs of x
-//     are pre-permuted in shared memory to match the register order, so no
-//     shuffles are needed; per-group scale/offset are applied in f32;
-//   * split-K inside a CTA is reduced through shared-memory atomics, split-K
-//     across CTAs through a thread-block cluster's distributed shared memory.
+//   * sixteen consumer warps own fixed sets of 64-input groups: nibbles / bytes
+//     are widened to bf16 in registers (one lop3 per two nibbles, 128 + q with
+//     the 128 folded into the offset term) and fed to mma.sync m16n8k16 with the
+//     batch as the 8-wide operand; the inputs of x are pre-permuted in shared
+//     memory to match the register order, so no shuffles are needed; per-group
+//     scale/offset are applied in f32;
+//   * the warps' partial tiles are added by rotating epilogue threads; a K split
+//     across CTAs goes through a thread-block cluster's distributed shared memory.
+// More than 32 rows: qmm_many.cu (dequantised panels in L2 + the tensor-core GEMM).
+// An alternative route for up to 8 rows on tcgen05: qmm_tc.cu (on request; slower, and why).
+// Tensor-parallel decoders: the `TP` builds of the kernel take part in the push exchange of
+// partial sums (tp.cuh); their slow paths are out of line, because these kernels pay about a
+// microsecond per launch for every 30-40 KB of code.
 #include <cooperative_groups.h>
 
 #include <algorithm>
