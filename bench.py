@@ -236,8 +236,8 @@ def build_device_model(pkg, cfg_local, batch, device, seed, world, rank, ctx):
 def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
     """The dequant-GEMV alone, in the forms the decode step launches it: every int4
     projection of the model back to back over its own weights (4 x layers distinct buffers,
-    far beyond L2), qkv and gate_up with the fused RMSNorm staging, o with the residual
-    epilogue, down with the fused silu(gate) * up staging and the residual epilogue."""
+    far beyond L2), qkv and gate_up with the fused RMSNorm staging, gate_up (on its row-interleaved
+    copy) forming silu(gate) * up in its epilogue, o and down with the residual epilogue."""
     import torch
     E, H, KV, D, I = (cfg_local[k] for k in ("hidden", "heads", "kv_heads", "head_dim", "inter"))
     bf = torch.bfloat16
@@ -246,17 +246,25 @@ def time_projection_kernels(pkg, params, cfg_local, batch, device, reps, ctx):
     x_gu = torch.randn((batch, 2 * I), device=device).to(bf)
     res = torch.randn((batch, E), device=device).to(bf)
     gain = torch.ones((E,), device=device, dtype=bf)
-    # (above 8 rows the decoder runs the RMSNorm as a kernel of its own, so the projection is launched plain)
+    # (above 8 rows the decoder runs the RMSNorm as a kernel of its own, so the projection is launched plain, and
+    # silu(gate) * up is formed while the down projection stages its input; up to 8 rows gate_up runs on its
+    # row-interleaved copy and forms silu(gate) * up in its epilogue, as the decoder does)
     norm = dict(rms_gain=gain) if batch <= 8 else {}
+    pair = batch <= 8 and I % 8 == 0
+    x_i = torch.randn((batch, I), device=device).to(bf)
     forms = {"qkv": lambda w: pkg.qwen3.linear(x_e, w, ctx=ctx, **norm),
              "o": lambda w: pkg.qwen3.linear(x_hd, w, residual=res, ctx=ctx),
-             "gate_up": lambda w: pkg.qwen3.linear(x_e, w, ctx=ctx, **norm),
-             "down": lambda w: pkg.qwen3.linear(x_gu, w, silu_mul=True, residual=res, ctx=ctx)}
+             "gate_up": (lambda w: pkg.qwen3.linear(x_e, w, silu_pair=True, ctx=ctx, **norm)) if pair
+                        else (lambda w: pkg.qwen3.linear(x_e, w, ctx=ctx, **norm)),
+             "down": (lambda w: pkg.qwen3.linear(x_i, w, residual=res, ctx=ctx)) if pair
+                     else (lambda w: pkg.qwen3.linear(x_gu, w, silu_mul=True, residual=res, ctx=ctx))}
     jobs, nbytes = [], 0
     for lp in params["layers"]:
         for name in ("qkv", "o", "gate_up", "down"):
             w = lp[name]
             n, k = w["q4"].shape[0], w["q4"].shape[1] * 8
+            if name == "gate_up" and pair:
+                w = pkg.qwen3.interleave_gate_up(w, ctx=ctx)
             jobs.append((forms[name], w))
             nbytes += n * k * 0.5625 + 2 * batch * (k + n)
     for f, w in jobs[:8]:

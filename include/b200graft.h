@@ -191,7 +191,10 @@ b200_status b200_matmul_execute(b200_context* ctx, b200_stream stream, const b20
 typedef enum { B200_QMM_OUT_BF16 = 0,      /* out bf16 [M, ldo] */
                B200_QMM_ADD_RESIDUAL = 1,  /* out = bf16(residual + bf16(y)), residual bf16 [M, ldo] */
                B200_QMM_OUT_F32 = 2,       /* out f32 [M, ldo] holding the bf16-rounded value */
-               B200_QMM_OUT_F32_RAW = 3    /* out f32 [M, ldo], unrounded (a partial sum of a K-sharded product) */
+               B200_QMM_OUT_F32_RAW = 3,   /* out f32 [M, ldo], unrounded (a partial sum of a K-sharded product) */
+               B200_QMM_OUT_SILU_PAIR = 4  /* the weight rows come as 8 gate rows then 8 up rows per 16 (b200_interleave_gate_up):
+                                              out bf16 [M, N/2] = silu(gate) * up with the reference's bf16 roundings
+                                              (qwen3.py:376), formed in the tile's epilogue; up to 8 rows of x */
 } b200_qmm_epilogue;
 
 /* Input transforms fused into the staging of x (each CTA applies them to the
@@ -225,6 +228,12 @@ typedef struct {
  * mma.sync kernel, 2 the tcgen05 kernel (nibbles spread to e4m3 bytes in tensor memory,
  * activations split into two e4m3 terms) wherever it applies.  For tests and measurements. */
 void b200_qmm_force_route(b200_context* ctx, int route);
+/* Rows of a [gate | up] projection (2 * inter rows: gate rows first, then up rows; any row size) rearranged so that
+ * every 16 consecutive rows hold 8 gate rows followed by the 8 up rows of the same outputs: what
+ * B200_QMM_OUT_SILU_PAIR consumes.  Applies to the packed weights and, with their row size, to the scale and offset
+ * rows.  inter a multiple of 8, row_bytes a multiple of 4; src and dst distinct. */
+b200_status b200_interleave_gate_up(b200_context* ctx, b200_stream stream, const void* src, void* dst, int64_t inter,
+                                    int64_t row_bytes);
 b200_status b200_qmm_validate(const b200_qmm_params* p);
 b200_status b200_qmm_run(b200_context* ctx, b200_stream stream, const b200_qmm_params* p);
 /* The short form: dense rows, bf16 in and out. */

@@ -15,7 +15,7 @@ STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "UNIMPLEMENTED", "INTERNAL", "RESOURCE
                 "FAILED_PRECONDITION", "TIMEOUT"]
 F32, F16, BF16 = 0, 1, 2
 ROUTE_NONE, ROUTE_TCGEN05, ROUTE_FEWROW, ROUTE_SIMT = 0, 1, 2, 3
-QMM_OUT_BF16, QMM_ADD_RESIDUAL, QMM_OUT_F32, QMM_OUT_F32_RAW = 0, 1, 2, 3
+QMM_OUT_BF16, QMM_ADD_RESIDUAL, QMM_OUT_F32, QMM_OUT_F32_RAW, QMM_OUT_SILU_PAIR = 0, 1, 2, 3, 4
 QMM_PRO_NONE, QMM_PRO_RMSNORM, QMM_PRO_SILU_MUL = 0, 1, 2
 KIND_RMS, KIND_SOFTMAX, KIND_LOG_SOFTMAX, KIND_LAYERNORM = 0, 1, 2, 3
 TP_ID_BYTES = 128
@@ -121,6 +121,7 @@ PROTOTYPES = {
     "b200_quantize": (_I, [_VP, _VP, _I, _I, _VP, _I, _VP, _VP, _VP, _I64, _I64]),
     "b200_quantize_int4_ref": (_I, [_VP, _VP, _VP, _I, _VP, _VP, _VP, _I64, _I64]),
     "b200_repack_int4": (_I, [_VP, _VP, _VP, _VP, _I64, _I64]),
+    "b200_interleave_gate_up": (_I, [_VP, _VP, _VP, _VP, _I64, _I64]),
     "b200_rownorm": (_I, [_VP, _VP, _I, _VP, _VP, _VP, _VP, _I64, _I64, _I, _D]),
     "b200_decoder_create": (_I, [_VP, C.POINTER(DecoderConfigC), C.POINTER(DecoderLayerC), _VP, _VP, _VP, _VP,
                                  C.POINTER(_VP)]),

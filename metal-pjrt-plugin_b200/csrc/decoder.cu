@@ -107,6 +107,11 @@ struct b200_decoder {
   std::map<int, int64_t> launches;
   std::mutex mu;                   // steps may come from several host threads
   DecodeStream* stream_path = nullptr;   // the single-kernel step, or null
+  // gate_up with its rows rearranged (8 gate rows, then the 8 up rows of the same outputs, per 16): with it the
+  // projection's epilogue forms silu(gate) * up itself, so the 148 CTAs of the down projection no longer each
+  // recompute all of it while staging their input.  One copy per layer, made at creation; empty: not in use.
+  std::vector<b200_qweight> gate_up_pair;
+  std::vector<void*> pair_storage;
 };
 
 namespace {
@@ -210,12 +215,13 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
       B200_TRY(Qmm(d, stream, L.o, d->attn, link.dst[link.rank], batch, E, HD, B200_QMM_OUT_F32_RAW, nullptr,
                    B200_QMM_PRO_NONE, nullptr, &to_peers));
       xp ^= 1;
-      B200_TRY(Qmm(d, stream, L.gate_up, xb[xp], d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
-                   nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm, &from_peers));
+      const bool pair = !d->gate_up_pair.empty();
+      B200_TRY(Qmm(d, stream, pair ? d->gate_up_pair[li] : L.gate_up, xb[xp], d->gu, batch, 2 * static_cast<int64_t>(c.inter), E,
+                   pair ? B200_QMM_OUT_SILU_PAIR : B200_QMM_OUT_BF16, nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm, &from_peers));
       to_peers.x_old = xb[xp];
       to_peers.x_out = xb[xp ^ 1];
       B200_TRY(Qmm(d, stream, L.down, d->gu, link.dst[link.rank], batch, E, c.inter, B200_QMM_OUT_F32_RAW, nullptr,
-                   B200_QMM_PRO_SILU_MUL, nullptr, &to_peers));
+                   pair ? B200_QMM_PRO_NONE : B200_QMM_PRO_SILU_MUL, nullptr, &to_peers));
       xp ^= 1;
       continue;
     }
@@ -240,7 +246,11 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
       if (!fuse_norm)
         B200_TRY(b200_rownorm(ctx, stream, 0, d->x, L.mlp_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
     }
-    if (fuse_norm)
+    const bool pair = fuse_norm && !tp && !d->gate_up_pair.empty();   // (the push flow above has its own use of it)
+    if (pair)
+      B200_TRY(Qmm(d, stream, d->gate_up_pair[li], d->x, d->gu, batch, 2 * static_cast<int64_t>(c.inter), E,
+                   B200_QMM_OUT_SILU_PAIR, nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm));
+    else if (fuse_norm)
       B200_TRY(Qmm(d, stream, L.gate_up, d->x, d->gu, batch, 2 * static_cast<int64_t>(c.inter), E, B200_QMM_OUT_BF16,
                    nullptr, B200_QMM_PRO_RMSNORM, L.mlp_norm));
     else
@@ -259,7 +269,7 @@ b200_status Enqueue(b200_decoder* d, cudaStream_t stream, const int32_t* tokens,
       B200_TRY(ResidualNorm(d, stream, next_norm, batch));
     } else {
       B200_TRY(Qmm(d, stream, L.down, d->gu, d->x, batch, E, c.inter, B200_QMM_ADD_RESIDUAL, d->x,
-                   B200_QMM_PRO_SILU_MUL));
+                   pair ? B200_QMM_PRO_NONE : B200_QMM_PRO_SILU_MUL));
       if (!fuse_norm)
         B200_TRY(b200_rownorm(ctx, stream, 0, d->x, next_norm, nullptr, d->h, batch, E, B200_BF16, c.rms_eps));
     }
@@ -381,6 +391,53 @@ b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cf
     b200_decoder_destroy(d);
     return s;
   }
+  // gate_up in the order its silu(gate) * up epilogue takes (up to 8 rows per step; plans without a K split)
+  if (!EnvFlag("B200_DECODER_NO_SILU_PAIR") && c.inter % 8 == 0 && c.hidden % 64 == 0) {
+    bool ok = true;
+    for (int m = 1; m <= std::min(c.max_batch, 8) && ok; ++m) {
+      b200_qmm_params pp = {};
+      pp.bits = 4;
+      pp.group = 64;
+      pp.epilogue = B200_QMM_OUT_BF16;
+      pp.prologue = B200_QMM_PRO_RMSNORM;
+      pp.M = m;
+      pp.N = 2 * static_cast<int64_t>(c.inter);
+      pp.K = c.hidden;
+      pp.x = pp.q = pp.scale = pp.bias = pp.prologue_gain = d->x;   // (placeholders: the plan looks at alignment only)
+      pp.out = d->x;
+      int rows = 0, split = 0, blocks = 0;
+      ok = b200_qmm_plan(&pp, &rows, &split, &blocks) == B200_OK && split == 1 && blocks == 1;
+    }
+    const int64_t rows = 2 * static_cast<int64_t>(c.inter), qb = c.hidden / 2, sb = c.hidden / 64 * 2;
+    for (int li = 0; ok && li < c.layers; ++li) {
+      void *q = nullptr, *sc = nullptr, *bi = nullptr;
+      cudaError_t ce = cudaMalloc(&q, rows * qb);
+      if (ce == cudaSuccess) d->pair_storage.push_back(q);
+      if (ce == cudaSuccess) ce = cudaMalloc(&sc, rows * sb);
+      if (ce == cudaSuccess) d->pair_storage.push_back(sc);
+      if (ce == cudaSuccess) ce = cudaMalloc(&bi, rows * sb);
+      if (ce == cudaSuccess) d->pair_storage.push_back(bi);
+      if (ce != cudaSuccess) {
+        (void)cudaGetLastError();
+        b200_decoder_destroy(d);
+        return Fail(B200_RESOURCE_EXHAUSTED, "b200_decoder_create: copy of gate_up for layer %d: %s", li, cudaGetErrorString(ce));
+      }
+      const b200_qweight& w = d->layers[li].gate_up;
+      s = b200_interleave_gate_up(ctx, nullptr, w.q, q, c.inter, qb);
+      if (s == B200_OK) s = b200_interleave_gate_up(ctx, nullptr, w.scale, sc, c.inter, sb);
+      if (s == B200_OK) s = b200_interleave_gate_up(ctx, nullptr, w.bias, bi, c.inter, sb);
+      if (s != B200_OK) {
+        b200_decoder_destroy(d);
+        return s;
+      }
+      b200_qweight pw = {q, sc, bi};
+      d->gate_up_pair.push_back(pw);
+    }
+    if (ok && cudaStreamSynchronize(nullptr) != cudaSuccess) {
+      b200_decoder_destroy(d);
+      return Stick(ctx, Fail(B200_INTERNAL, "b200_decoder_create: rearranging gate_up failed"));
+    }
+  }
   // B200_DECODER_STREAM=1 selects the single persistent kernel where it applies.  It is not the
   // default: measured on the Qwen3-8B shape it takes 2.5 ms per step at batch 1 against 2.2 ms
   // for the captured kernel-per-operator graph (its grid barriers and input staging cost what
@@ -411,6 +468,7 @@ void b200_decoder_destroy(b200_decoder* d) {
                   static_cast<void*>(d->logits_bf16), static_cast<void*>(d->x2), static_cast<void*>(d->tokens_buf),
                   static_cast<void*>(d->pos_buf)})
     if (p != nullptr) cudaFree(p);
+  for (void* p : d->pair_storage) cudaFree(p);
   delete d;
 }
 

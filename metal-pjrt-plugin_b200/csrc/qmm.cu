@@ -1018,7 +1018,24 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         if (partials) {
           // the epilogue moves to other warps every tile, so no warp is always the late one
           const int et = (tid + kConsumerThreads - ((ti * 128) % kConsumerThreads)) % kConsumerThreads;
-          if (et < rows_valid * a.M) {
+          if (a.epilogue == B200_QMM_OUT_SILU_PAIR) {
+            // rows come as 8 gate rows then 8 up rows per 16: out[m, n0 / 2 + pair] = silu(gate) * up, with the
+            // reference's bf16 roundings (the projection's own output, the sigmoid, gate * sigmoid, the product)
+            if (et < (rows_valid / 2) * a.M) {
+              const int pr = et % (rows_valid / 2), m = et / (rows_valid / 2);
+              const int rg = (pr >> 3) * 16 + (pr & 7);
+              float vg = 0.0f, vu = 0.0f;
+#pragma unroll
+              for (int w = 0; w < kConsumerWarps; ++w) {
+                vg += red_cur[(w * R + rg) * MP + m];
+                vu += red_cur[(w * R + rg + 8) * MP + m];
+              }
+              const float g = bf16_round(vg), u = bf16_round(vu);
+              const float sig = bf16_round(__fdividef(1.0f, 1.0f + __expf(-g)));
+              reinterpret_cast<__nv_bfloat16*>(a.out)[static_cast<size_t>(m) * a.ldo + n0 / 2 + pr] =
+                  __float2bfloat16_rn(bf16_round(g * sig) * u);
+            }
+          } else if (et < rows_valid * a.M) {
             const int r = et % rows_valid, m = et / rows_valid;
             float v = 0.0f;
 #pragma unroll
@@ -1124,7 +1141,9 @@ b200_status Validate(const b200_qmm_params* p) {
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: int8 group must be 64 or K, got %d", p->group);
   if (p->bits == 4 && p->nibble_order != 0 && p->nibble_order != 1)
     return Fail(B200_INVALID_ARGUMENT, "b200_qmm: nibble_order must be 0 or 1");
-  if (p->epilogue < 0 || p->epilogue > 3) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: unknown epilogue %d", p->epilogue);
+  if (p->epilogue < 0 || p->epilogue > 4) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: unknown epilogue %d", p->epilogue);
+  if (p->epilogue == B200_QMM_OUT_SILU_PAIR && (p->M > 8 || p->N % 16 != 0 || p->bits == 16 || (p->bits == 8 && p->group != 64)))
+    return Fail(B200_UNIMPLEMENTED, "b200_qmm: the silu(gate) * up epilogue takes up to 8 rows of x and grouped weights with N a multiple of 16");
   if (p->prologue < 0 || p->prologue > 2) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: unknown prologue %d", p->prologue);
   if (p->prologue == B200_QMM_PRO_RMSNORM && p->M > 8)
     return Fail(B200_UNIMPLEMENTED, "b200_qmm: the fused RMSNorm takes up to 8 rows (run b200_rownorm first)");
@@ -1138,8 +1157,9 @@ b200_status Validate(const b200_qmm_params* p) {
     return Fail(B200_INVALID_ARGUMENT, "b200_qmm: residual epilogue without a residual buffer");
   if (!Aligned(p->q, 16)) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: q must be 16-byte aligned (bulk copies)");
   const int64_t xcols = p->prologue == B200_QMM_PRO_SILU_MUL ? 2 * p->K : p->K;
-  const int64_t ldx = p->ldx ? p->ldx : xcols, ldo = p->ldo ? p->ldo : p->N;
-  if (ldx < xcols || ldo < p->N) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: leading dimension smaller than row length");
+  const int64_t ncols = p->epilogue == B200_QMM_OUT_SILU_PAIR ? p->N / 2 : p->N;
+  const int64_t ldx = p->ldx ? p->ldx : xcols, ldo = p->ldo ? p->ldo : ncols;
+  if (ldx < xcols || ldo < ncols) return Fail(B200_INVALID_ARGUMENT, "b200_qmm: leading dimension smaller than row length");
   if (p->K == 0) return Fail(B200_UNIMPLEMENTED, "b200_qmm: K = 0");
   return B200_OK;
 }
@@ -1419,7 +1439,16 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
     return QmmManyRows(ctx, stream, p);
   }
   const int forced = ctx->qmm_route.load();
-  if ((tp == nullptr || tp->world <= 1) && (forced == 2 || (forced == 0 && TcRouteEnabled())) && QmmTcEligible(ctx, p))
+  if (p->epilogue == B200_QMM_OUT_SILU_PAIR) {
+    Plan chk;
+    b200_status ps = MakePlan(p, ctx->sm_count, ctx->max_smem_optin, &chk);
+    if (ps != B200_OK) return ps;
+    if (chk.split != 1 || chk.mb != 1)
+      return Fail(B200_UNIMPLEMENTED, "b200_qmm: the silu(gate) * up epilogue needs a plan without a K split (M=%lld N=%lld K=%lld)",
+                  static_cast<long long>(p->M), static_cast<long long>(p->N), static_cast<long long>(p->K));
+  }
+  if ((tp == nullptr || tp->world <= 1) && p->epilogue != B200_QMM_OUT_SILU_PAIR && (forced == 2 || (forced == 0 && TcRouteEnabled())) &&
+      QmmTcEligible(ctx, p))
     return QmmTcRun(ctx, stream, p);
   Plan pl;
   s = MakePlan(p, ctx->sm_count, ctx->max_smem_optin, &pl);
@@ -1435,7 +1464,7 @@ b200_status QmmRunEx(b200_context* ctx, cudaStream_t stream, const b200_qmm_para
   a.N = static_cast<int>(p->N);
   a.K = static_cast<int>(p->K);
   a.ldx = static_cast<int>(p->ldx ? p->ldx : (p->prologue == B200_QMM_PRO_SILU_MUL ? 2 * p->K : p->K));
-  a.ldo = static_cast<int>(p->ldo ? p->ldo : p->N);
+  a.ldo = static_cast<int>(p->ldo ? p->ldo : (p->epilogue == B200_QMM_OUT_SILU_PAIR ? p->N / 2 : p->N));
   a.prologue = p->prologue;
   a.eps = p->eps;
   a.gain = static_cast<const __nv_bfloat16*>(p->prologue_gain);

@@ -134,6 +134,18 @@ __global__ void repack_int4_kernel(const uint8_t* in, uint32_t* out, int64_t wor
   }
 }
 
+// dst row d = 16 t + j: gate row 8 t + j (j < 8) or up row 8 t + j - 8, i.e. source row inter + 8 t + j - 8.
+__global__ void interleave_gate_up_kernel(const uint32_t* src, uint32_t* dst, int64_t inter, int64_t row_words) {
+  const int64_t total = 2 * inter * row_words;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t d = i / row_words, w = i % row_words;
+    const int64_t t = d >> 4, j = d & 15;
+    const int64_t srow = j < 8 ? 8 * t + j : inter + 8 * t + (j - 8);
+    dst[i] = src[srow * row_words + w];
+  }
+}
+
 // One warp per (row, group): symmetric int8.
 template <typename T>
 __global__ void quantize_int8_kernel(const T* w, int8_t* q, __nv_bfloat16* scale, int64_t N, int64_t K, int group) {
@@ -260,6 +272,22 @@ b200_status b200_repack_int4(b200_context* ctx, b200_stream stream, const void* 
   const int blocks = static_cast<int>(std::min<int64_t>(CeilDiv(words, 256), 148 * 16));
   repack_int4_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(q_split_half), static_cast<uint32_t*>(q_sequential), words);
   return EndLaunch(ctx, "b200_repack_int4");
+}
+
+b200_status b200_interleave_gate_up(b200_context* ctx, b200_stream stream, const void* src, void* dst, int64_t inter,
+                                    int64_t row_bytes) {
+  b200_status s = BeginLaunch(ctx);
+  if (s != B200_OK) return s;
+  if (inter < 0 || row_bytes < 0) return Fail(B200_INVALID_ARGUMENT, "b200_interleave_gate_up: negative size");
+  if (inter == 0 || row_bytes == 0) return B200_OK;
+  if (inter % 8 != 0 || row_bytes % 4 != 0)
+    return Fail(B200_UNIMPLEMENTED, "b200_interleave_gate_up: inter must be a multiple of 8 and rows a multiple of 4 bytes");
+  if (src == nullptr || dst == nullptr || src == dst || !Aligned(src, 4) || !Aligned(dst, 4))
+    return Fail(B200_INVALID_ARGUMENT, "b200_interleave_gate_up: null, aliased or unaligned buffer");
+  const int64_t total = 2 * inter * (row_bytes / 4);
+  const int blocks = static_cast<int>(std::min<int64_t>(CeilDiv(total, 256), 148 * 32));
+  interleave_gate_up_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), inter, row_bytes / 4);
+  return EndLaunch(ctx, "b200_interleave_gate_up");
 }
 
 }  // extern "C"

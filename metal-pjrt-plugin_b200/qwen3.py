@@ -80,7 +80,25 @@ def dequantize(w, dtype=None, ctx=None):
     return out
 
 
-def linear(x, w, residual=None, out_f32=False, rms_gain=None, eps=1e-6, silu_mul=False, ctx=None, stream=None):
+def interleave_gate_up(w, ctx=None):
+    """A quantised [gate | up] projection with its rows rearranged for linear(..., silu_pair=True):
+    every 16 consecutive rows hold 8 gate rows, then the 8 up rows of the same outputs."""
+    torch = _torch()
+    first = next(iter(w.values()))
+    ctx = ctx or default_context(first.device.index or 0)
+    out = {}
+    for k, v in w.items():
+        v = v.contiguous()
+        rows = v.shape[0]
+        o = torch.empty_like(v)
+        _lib.check(_lib.lib().b200_interleave_gate_up(ctx.handle, _lib.current_stream(), _lib.ptr(v), _lib.ptr(o), rows // 2,
+                                                     v.numel() // rows * v.element_size()))
+        out[k] = o
+    return out
+
+
+def linear(x, w, residual=None, out_f32=False, rms_gain=None, eps=1e-6, silu_mul=False, silu_pair=False, ctx=None,
+           stream=None):
     """≙ linear (qwen3.py:218-230): x @ w.T for an [out, in] weight, bf16 or
     quantised, up to ROWS_MAX rows; result in x's dtype (bf16).  `residual`
     fuses the x + linear(...) of the decoder layer; out_f32 gives the LM head's
@@ -92,23 +110,26 @@ def linear(x, w, residual=None, out_f32=False, rms_gain=None, eps=1e-6, silu_mul
     lead = x.shape[:-1]
     x2 = x.reshape(-1, 2 * K if silu_mul else K)
     M = x2.shape[0]
-    out = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    n_out = N // 2 if silu_pair else N   # silu_pair: w from interleave_gate_up; the result is silu(gate) * up
+    out = torch.empty((M, n_out), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     p = _lib.QmmParamsC()
     p.bits, p.group, p.nibble_order = bits, group, order
     p.epilogue = _lib.QMM_OUT_F32 if out_f32 else (_lib.QMM_ADD_RESIDUAL if residual is not None else _lib.QMM_OUT_BF16)
+    if silu_pair:
+        p.epilogue = _lib.QMM_OUT_SILU_PAIR
     p.x, p.q = x2.data_ptr(), q.data_ptr()
     p.scale = s.data_ptr() if s is not None else None
     p.bias = b.data_ptr() if b is not None else None
     p.residual = residual.data_ptr() if residual is not None else None
     p.out = out.data_ptr()
     p.M, p.N, p.K = M, N, K
-    p.ldx, p.ldo = x2.stride(0) if M > 0 else 0, N
+    p.ldx, p.ldo = x2.stride(0) if M > 0 else 0, n_out
     if rms_gain is not None:
         p.prologue, p.eps, p.prologue_gain = _lib.QMM_PRO_RMSNORM, eps, rms_gain.data_ptr()
     elif silu_mul:
         p.prologue = _lib.QMM_PRO_SILU_MUL
     _lib.check(_lib.lib().b200_qmm_run(ctx.handle, stream or _lib.current_stream(), C.byref(p)))
-    return out.reshape(*lead, N)
+    return out.reshape(*lead, n_out)
 
 
 def qmm_plan(M, N, K, bits=4, group=64):

@@ -354,3 +354,38 @@ def test_int8_one_hot_unpack(group, m, k):
     dense = quant.dequant_f32(q, s, None, group or k)
     ks = [0, 1, 15, 16, 63, 64, 127, 128, 1023, 1024, 2047, 2048, k // 2, k - 129, k - 128, k - 64, k - 1][:m]
     _one_hot_check(p, {"q": dev(q), "s": dev(s)}, dense, k, ks, m)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("k,inter,fuse_norm", [(1024, 768, False), (1024, 768, True), (4096, 12288, True)])
+def test_silu_pair_epilogue(m, k, inter, fuse_norm):
+    """gate_up on its row-interleaved copy with silu(gate) * up formed in the projection's epilogue:
+    equal to the two-step form (projection to bf16, then silu_mul) on the same weights."""
+    from oracle import decoder as odec
+    from oracle import rownorm
+    p = pkg()
+    x, packed, s, b, _ = inputs.config4(m, k, 2 * inter)
+    w = _w4(packed, s, b)
+    wp = p.qwen3.interleave_gate_up(w)
+    gain = (1 + 0.1 * np.random.default_rng(3).standard_normal(k, dtype=np.float32)).astype(bf16)
+    kw = dict(rms_gain=dev(gain), eps=1e-6) if fuse_norm else {}
+    got = host(p.qwen3.linear(dev(x), wp, silu_pair=True, **kw))
+    assert got.shape == (m, inter)
+    # the device's own two-step form: same sums, same roundings
+    gu = p.qwen3.linear(dev(x), w, **kw)
+    two = host(gu).astype(np.float32)
+    want_dev = odec.silu_mul(two[:, :inter].astype(bf16), two[:, inter:].astype(bf16))
+    ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want_dev.astype(np.float32)), 1e-30))) - 7)
+    assert np.all(np.abs(got.astype(np.float32) - want_dev.astype(np.float32)) <= 1.01 * ulp)
+    # and against the oracle end to end (a sample of columns at full size)
+    cols = np.random.default_rng(0).choice(inter, min(inter, 256), replace=False)
+    h = rownorm.rms_norm(x, gain, 1e-6) if fuse_norm else x
+    rows = np.concatenate([cols, inter + cols])
+    q = quant.bl_unpack_int4(packed[rows])
+    gu_ref = quant.qmm(h, q, s[rows], b[rows], bf16)
+    want = odec.silu_mul(gu_ref[:, :len(cols)], gu_ref[:, len(cols):]).astype(np.float32)
+    assert rel_rms_err(got.astype(np.float32)[:, cols], want) <= 3e-2
+    # the rows of the copy are the original's, rearranged
+    qp = host(wp["q4"]).view(np.uint32)
+    assert np.array_equal(qp[0:8], packed[0:8]) and np.array_equal(qp[8:16], packed[inter:inter + 8])
+    assert np.array_equal(qp[16:24], packed[8:16])
