@@ -314,7 +314,11 @@ typedef struct b200_decoder b200_decoder;
 typedef struct b200_tp b200_tp;
 
 /* cfg holds this rank's LOCAL head counts / inter / vocab share; `tp` may be NULL
- * (one GPU).  The layer structs are copied; the buffers they point to are borrowed. */
+ * (one GPU).  The layer structs are copied; the buffers they point to are borrowed.
+ * The decoder owns its activation buffers and, for steps of up to 8 rows, one
+ * row-interleaved copy of every gate_up matrix (b200_interleave_gate_up; the size of the
+ * original), with which that projection forms silu(gate) * up in its epilogue;
+ * B200_DECODER_NO_SILU_PAIR=1 leaves the copies out. */
 b200_status b200_decoder_create(b200_context* ctx, const b200_decoder_config* cfg,
                                 const b200_decoder_layer* layers, const void* embed /* bf16 [vocab_full, hidden] */,
                                 const void* final_norm, const void* lm_head /* bf16 [vocab, hidden] */,
