@@ -129,6 +129,11 @@ def test_qmm_validate_and_plan():
     assert v(q(ptr=None)) == L.INVALID_ARGUMENT
     assert v(q(ptr=4100)) == L.INVALID_ARGUMENT     # packed weights must be 16-byte aligned
     assert v(q(epi=1)) == L.INVALID_ARGUMENT        # residual epilogue without a residual
+    assert v(q(epi=4, N=24576)) == L.OK             # silu(gate) * up in the epilogue of a row-interleaved gate_up
+    assert v(q(epi=4, N=24584)) == L.UNIMPLEMENTED  # ... whose rows come in sixteens
+    assert v(q(epi=4, M=9)) == L.UNIMPLEMENTED      # ... for up to 8 rows of x
+    assert v(q(epi=4, bits=16)) == L.UNIMPLEMENTED
+    assert v(q(epi=5)) == L.INVALID_ARGUMENT
     # plans: tiles grow with the batch block count; small matrices split K across a cluster
     plan = p.qwen3.qmm_plan
     assert plan(1, 4096, 4096) == (32, 1, 1)       # one 32-row tile for 128 CTAs costs the busiest SM what two 16-row tiles would
