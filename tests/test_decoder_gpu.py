@@ -333,6 +333,36 @@ def test_step_replay_is_deterministic(step_path):
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("batch", [1, 4, 8])
+def test_silu_in_the_gate_up_epilogue_equals_the_two_step_form(batch, monkeypatch):
+    """The decoder with silu(gate) * up formed in the gate_up projection's epilogue (on its row-interleaved
+    copy of the weights) and the one that forms it while the down projection stages its input: the same
+    sums and the same roundings, so the same logits and the same cache rows, bit for bit."""
+    import torch
+    monkeypatch.delenv("B200_DECODER_STREAM", raising=False)
+    cfg = inputs.decoder_config(layers=3, hidden=256, heads=4, kv_heads=2, head_dim=64, inter=512, vocab=1024)
+    p = pkg()
+    params, cache, tokens = inputs.config5(cfg, batch, 20, max_len=32)
+    tok = dev(tokens.astype(np.int32))
+    pos = torch.tensor([20], dtype=torch.int32, device="cuda")
+    outs, caches = [], []
+    for no_pair in (False, True):
+        if no_pair:
+            monkeypatch.setenv("B200_DECODER_NO_SILU_PAIR", "1")
+        else:
+            monkeypatch.delenv("B200_DECODER_NO_SILU_PAIR", raising=False)
+        dcache = {k: [dev(a) for a in v] for k, v in cache.items()}
+        dec = p.qwen3.Decoder(dev_params(params), dcache, cfg, max_batch=batch)
+        outs.append(dec.step(tok, pos).clone())
+        torch.cuda.synchronize()
+        caches.append(dcache)
+        dec.close()
+    assert torch.equal(outs[0], outs[1])
+    for a, b in zip(caches[0]["k"] + caches[0]["v"], caches[1]["k"] + caches[1]["v"]):
+        assert torch.equal(a, b)
+    assert p.default_context().error() == 0
+
+
 def test_fresh_tensors_every_step_do_not_grow_the_graph_cache(monkeypatch):
     """A generate loop hands the step new token / position tensors every time and often a new
     logits tensor: tokens and position are staged, graphs are keyed by the output pointer and
