@@ -479,7 +479,7 @@ def run_ours(args):
                      "achieved_gbs_per_gpu": total_bytes / world / (t_dev / args.steps) / 1e9,
                      "frac_of_peak": total_bytes / world / (t_dev / args.steps) / 1e9 / peak},
         "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (int4-g64 dequant-GEMV: all 4 x layers projections as the decode step "
-                                               "launches them, fused RMSNorm / silu(gate)*up staging and residual epilogue included)",
+                                               "launches them: fused RMSNorm staging, silu(gate)*up and residual epilogues included)",
                      "achieved": achieved, "peak": peak, "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s",
                      "frac": achieved / peak, "frac_of_nominal_8tbs": achieved / 8000.0,
                      "algorithmic_bytes_per_launch": bytes_per_launch, "us_per_launch": sec_per_launch * 1e6,
